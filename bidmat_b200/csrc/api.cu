@@ -1,0 +1,500 @@
+// Host side of the C ABI declared in include/bidmat_b200.h: argument checks,
+// kernel selection by the dense height k, the per-device scratch workspace and
+// the row-sort that turns the CSC nonzero list into the row-major order B*^S
+// needs.  Built for sm_100a only.
+#include <cuda_runtime.h>
+#include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_reduce.cuh>
+
+#include <atomic>
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "../../include/bidmat_b200.h"
+#include "kernels.cuh"
+
+using namespace bidmat;
+
+namespace {
+
+std::atomic<long long> g_launches{0};
+
+// ------------------------------------------------------------------ timing
+// Optional per-kernel timing for the benchmark: when enabled, the launchers
+// bracket their main kernels with CUDA events on the launching stream.
+struct TimedSpan { const char *label; cudaEvent_t a, b; };
+std::atomic<int> g_timing{0};
+std::mutex g_span_mu;
+std::vector<TimedSpan> g_spans;
+
+struct ScopedSpan {
+    cudaStream_t st;
+    TimedSpan span{nullptr, nullptr, nullptr};
+    ScopedSpan(const char *label, cudaStream_t s) : st(s) {
+        if (!g_timing.load()) return;
+        if (cudaEventCreate(&span.a) != cudaSuccess || cudaEventCreate(&span.b) != cudaSuccess) return;
+        span.label = label;
+        cudaEventRecord(span.a, st);
+    }
+    ~ScopedSpan() {
+        if (!span.label) return;
+        cudaEventRecord(span.b, st);
+        std::lock_guard<std::mutex> g(g_span_mu);
+        g_spans.push_back(span);
+    }
+};
+
+// ------------------------------------------------------------------ workspace
+// One grow-only scratch buffer per device.  Calls on one device are serialised
+// by the mutex for their host part and ordered on the device by an event, so
+// two streams can never use the buffer at the same time.
+struct Workspace {
+    std::mutex mu;
+    void *ptr = nullptr;
+    size_t bytes = 0;
+    cudaEvent_t last_use = nullptr;
+};
+constexpr int kMaxDevices = 64;
+Workspace g_ws[kMaxDevices];
+
+struct WorkspaceLease {
+    Workspace *ws = nullptr;
+    cudaStream_t stream = nullptr;
+    char *base = nullptr;
+    size_t used = 0;
+    cudaError_t err = cudaSuccess;
+
+    WorkspaceLease(size_t bytes, cudaStream_t s) : stream(s) {
+        int dev = 0;
+        err = cudaGetDevice(&dev);
+        if (err != cudaSuccess) return;
+        if (dev < 0 || dev >= kMaxDevices) { err = cudaErrorInvalidDevice; return; }
+        ws = &g_ws[dev];
+        ws->mu.lock();
+        if (ws->last_use == nullptr) {
+            err = cudaEventCreateWithFlags(&ws->last_use, cudaEventDisableTiming);
+            if (err != cudaSuccess) return;
+        } else {
+            err = cudaStreamWaitEvent(stream, ws->last_use, 0);
+            if (err != cudaSuccess) return;
+        }
+        if (bytes > ws->bytes) {
+            if (ws->ptr) {
+                err = cudaDeviceSynchronize();
+                if (err != cudaSuccess) return;
+                cudaFree(ws->ptr);
+                ws->ptr = nullptr;
+                ws->bytes = 0;
+            }
+            size_t want = bytes + bytes / 8 + (1u << 20);
+            err = cudaMalloc(&ws->ptr, want);
+            if (err != cudaSuccess) { ws->ptr = nullptr; return; }
+            ws->bytes = want;
+        }
+        base = static_cast<char *>(ws->ptr);
+    }
+    template <typename T> T *take(size_t count) {
+        size_t off = (used + 255) & ~size_t(255);
+        used = off + count * sizeof(T);
+        return reinterpret_cast<T *>(base + off);
+    }
+    ~WorkspaceLease() {
+        if (ws) {
+            if (ws->last_use) cudaEventRecord(ws->last_use, stream);
+            ws->mu.unlock();
+        }
+    }
+};
+
+inline size_t pad256(size_t b) { return (b + 255) & ~size_t(255); }
+
+// ------------------------------------------------------------------ shapes
+// How a dense column of height k is spread over a worker.
+struct Shape {
+    int vec;   // 4 when k % 4 == 0 and the pointers are 16-byte aligned, else 1
+    int lpv;   // lanes per worker
+    int nt;    // VEC-wide elements per lane
+    int tiles; // k-tiles of width lpv*nt*vec
+};
+
+Shape pick_shape(int k, bool aligned16) {
+    Shape s;
+    s.vec = (aligned16 && (k % 4 == 0)) ? 4 : 1;
+    const int kv = k / s.vec;
+    if (kv <= 8) { s.lpv = 8; s.nt = 1; }
+    else if (kv <= 16) { s.lpv = 16; s.nt = 1; }
+    else if (kv <= 32) { s.lpv = 32; s.nt = 1; }
+    else if (kv <= 64) { s.lpv = 32; s.nt = 2; }
+    else { s.lpv = 32; s.nt = 4; }
+    const int tile = s.lpv * s.nt * s.vec;
+    s.tiles = (k + tile - 1) / tile;
+    return s;
+}
+
+bool is16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int env_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    if (!v || !*v) return dflt;
+    return atoi(v);
+}
+
+// Chunk length: aim at about 64K chunks so that the hardware scheduler can
+// balance them over 148 SMs, but never fewer than 64 nor more than 4096
+// nonzeros per chunk.  BIDMAT_B200_CHUNK overrides (tests use tiny chunks to
+// force runs across chunk boundaries).
+int pick_chunk(long long nnz, int lpv) {
+    int forced = env_int("BIDMAT_B200_CHUNK", 0);
+    long long c;
+    if (forced > 0) c = forced;
+    else {
+        c = (nnz + 65535) / 65536;
+        if (c < 64) c = 64;
+        if (c > 4096) c = 4096;
+    }
+    c = ((c + lpv - 1) / lpv) * lpv;
+    return (int)c;
+}
+
+#define DISPATCH_SHAPE(S, CALL)                                                     \
+    do {                                                                            \
+        if ((S).vec == 4) {                                                         \
+            if ((S).lpv == 8) { CALL(4, 8, 1); }                                    \
+            else if ((S).lpv == 16) { CALL(4, 16, 1); }                             \
+            else if ((S).nt == 1) { CALL(4, 32, 1); }                               \
+            else if ((S).nt == 2) { CALL(4, 32, 2); }                               \
+            else { CALL(4, 32, 4); }                                                \
+        } else {                                                                    \
+            if ((S).lpv == 8) { CALL(1, 8, 1); }                                    \
+            else if ((S).lpv == 16) { CALL(1, 16, 1); }                             \
+            else if ((S).nt == 1) { CALL(1, 32, 1); }                               \
+            else if ((S).nt == 2) { CALL(1, 32, 2); }                               \
+            else { CALL(1, 32, 4); }                                                \
+        }                                                                           \
+    } while (0)
+
+unsigned blocks_for(long long workers, int lpv) {
+    long long threads = workers * lpv;
+    return (unsigned)((threads + kThreads - 1) / kThreads);
+}
+
+// O[:, seg[j]] += val[j] * D[:, gidx[j]] with `part` holding 2*nchunks*k floats.
+cudaError_t launch_ga(int k, long long nnz, const float *D, const float *val, const int *gidx,
+                      const int *seg, float *O, float *part, int chunk, const Shape &s,
+                      cudaStream_t st, const char *label) {
+    const long long nchunks = (nnz + chunk - 1) / chunk;
+    dim3 grid(blocks_for(nchunks, s.lpv), s.tiles, 1);
+#define CALL_GA(VEC, LPV, NT)                                                                   \
+    {                                                                                           \
+        ScopedSpan sp(label, st);                                                               \
+        ga_chunk_kernel<VEC, LPV, NT, 4><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, D, val, \
+                                                                    gidx, seg, O, part);        \
+    }                                                                                           \
+    if (nchunks > 1) {                                                                          \
+        ScopedSpan sp("ga_fixup", st);                                                          \
+        ga_fixup_kernel<VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, seg, O, part); \
+    }
+    DISPATCH_SHAPE(s, CALL_GA);
+#undef CALL_GA
+    g_launches += (nchunks > 1) ? 2 : 1;
+    return cudaGetLastError();
+}
+
+size_t ga_part_floats(int k, long long nnz, int chunk) {
+    const long long nchunks = (nnz + chunk - 1) / chunk;
+    return (size_t)nchunks * 2 * (size_t)k;
+}
+
+template <bool ACCUM>
+cudaError_t launch_dds(int k, long long nnz, const float *A, const float *B, const int *ir,
+                       const int *ic, float *P, cudaStream_t st) {
+    const Shape s = pick_shape(k, is16(A) && is16(B));
+    const int chunk = pick_chunk(nnz, s.lpv);
+    const long long nchunks = (nnz + chunk - 1) / chunk;
+    dim3 grid(blocks_for(nchunks, s.lpv), 1, 1);
+    ScopedSpan sp("dds_chunk", st);
+#define CALL_DDS(VEC, LPV, NT)                                                                  \
+    dds_chunk_kernel<VEC, LPV, NT, 4, ACCUM><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, A, B, \
+                                                                        ir, ic, P);
+    DISPATCH_SHAPE(s, CALL_DDS);
+#undef CALL_DDS
+    g_launches += 1;
+    return cudaGetLastError();
+}
+
+inline cudaStream_t as_stream(bidmat_stream_t s) {
+    return s ? static_cast<cudaStream_t>(s) : cudaStreamPerThread;
+}
+
+inline int finish_sync(cudaError_t err, cudaStream_t st) {
+    if (err != cudaSuccess) return (int)err;
+    err = cudaStreamSynchronize(st);
+    if (err != cudaSuccess) return (int)err;
+    return (int)cudaGetLastError();
+}
+
+int ceil_log2(unsigned long long v) {  // smallest b with 2^b >= v (v >= 1)
+    int b = 0;
+    while ((1ull << b) < v) b++;
+    return b;
+}
+
+}  // namespace
+
+extern "C" {
+
+int bidmat_b200_dsmult_async(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                             const int *Bir, const int *Bic, float *C, bidmat_stream_t stream) {
+    if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (nnz == 0 || nrows == 0) return 0;
+    if (!A || !Bdata || !Bir || !Bic || !C) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = as_stream(stream);
+    const Shape s = pick_shape(nrows, is16(A) && is16(C));
+    const int chunk = pick_chunk(nnz, s.lpv);
+    WorkspaceLease ws(pad256(ga_part_floats(nrows, nnz, chunk) * sizeof(float)) + 256, st);
+    if (ws.err != cudaSuccess) return (int)ws.err;
+    float *part = ws.take<float>(ga_part_floats(nrows, nnz, chunk));
+    return (int)launch_ga(nrows, nnz, A, Bdata, Bir, Bic, C, part, chunk, s, st, "dsmult_ga_chunk");
+}
+
+int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                              const int *Bir, const int *Bic, float *C, int m_hint,
+                              bidmat_stream_t stream) {
+    if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (nnz == 0 || nrows == 0) return 0;
+    if (!A || !Bdata || !Bir || !Bic || !C) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = as_stream(stream);
+    const size_t n = (size_t)nnz;
+    const Shape s = pick_shape(nrows, is16(A) && is16(C));
+    const int chunk = pick_chunk(nnz, s.lpv);
+
+    size_t sort_tmp = 0, red_tmp = 0;
+    cudaError_t err = cub::DeviceRadixSort::SortPairs(nullptr, sort_tmp, (const int *)nullptr, (int *)nullptr,
+                                                      (const int *)nullptr, (int *)nullptr, n, 0, 32, st);
+    if (err != cudaSuccess) return (int)err;
+    err = cub::DeviceReduce::Max(nullptr, red_tmp, (const int *)nullptr, (int *)nullptr, n, st);
+    if (err != cudaSuccess) return (int)err;
+    const size_t tmp_bytes = sort_tmp > red_tmp ? sort_tmp : red_tmp;
+    const size_t part_floats = ga_part_floats(nrows, nnz, chunk);
+    size_t need = pad256(tmp_bytes) + 5 * pad256(n * 4) + pad256(part_floats * 4) + 1024;
+    WorkspaceLease ws(need, st);
+    if (ws.err != cudaSuccess) return (int)ws.err;
+    char *tmp = ws.take<char>(tmp_bytes);
+    int *iota = ws.take<int>(n);
+    int *rows_sorted = ws.take<int>(n);
+    int *perm = ws.take<int>(n);
+    int *cols_sorted = ws.take<int>(n);
+    float *vals_sorted = ws.take<float>(n);
+    float *part = ws.take<float>(part_floats);
+    int *maxrow = ws.take<int>(1);
+
+    int bits = 32;
+    if (m_hint > 0) {
+        bits = ceil_log2((unsigned long long)m_hint);
+    } else {
+        size_t t = tmp_bytes;
+        err = cub::DeviceReduce::Max(tmp, t, Bir, maxrow, n, st);
+        if (err != cudaSuccess) return (int)err;
+        int h = 0;
+        err = cudaMemcpyAsync(&h, maxrow, sizeof(int), cudaMemcpyDeviceToHost, st);
+        if (err != cudaSuccess) return (int)err;
+        err = cudaStreamSynchronize(st);
+        if (err != cudaSuccess) return (int)err;
+        if (h < 0) return (int)cudaErrorInvalidValue;
+        bits = ceil_log2((unsigned long long)h + 1);
+    }
+    if (bits < 1) bits = 1;
+    if (bits > 31) bits = 31;
+
+    const unsigned nb = (unsigned)((n + kThreads - 1) / kThreads);
+    ScopedSpan *sort_span = new ScopedSpan("dsmultT_rowsort", st);
+    iota_kernel<<<nb, kThreads, 0, st>>>(nnz, iota);
+    g_launches += 1;
+    size_t t = tmp_bytes;
+    // Stable LSD radix sort by row: equal rows keep ascending nonzero order,
+    // i.e. ascending source column, the order the reference CPU loop adds in.
+    err = cub::DeviceRadixSort::SortPairs(tmp, t, Bir, rows_sorted, iota, perm, n, 0, bits, st);
+    if (err != cudaSuccess) { delete sort_span; return (int)err; }
+    permute_pairs_kernel<<<nb, kThreads, 0, st>>>(nnz, perm, Bic, Bdata, cols_sorted, vals_sorted);
+    g_launches += 1;
+    delete sort_span;
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return (int)err;
+    return (int)launch_ga(nrows, nnz, A, vals_sorted, cols_sorted, rows_sorted, C, part, chunk, s, st, "dsmultT_ga_chunk");
+}
+
+int bidmat_b200_dds_async(int nrows, int nnz, const float *A, const float *B, const int *Cir,
+                          const int *Cic, float *P, bidmat_stream_t stream) {
+    if (nrows < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (nnz == 0) return 0;
+    if (!A || !B || !Cir || !Cic || !P) return (int)cudaErrorInvalidValue;
+    if (nrows == 0) return 0;
+    return (int)launch_dds<true>(nrows, nnz, A, B, Cir, Cic, P, as_stream(stream));
+}
+
+int bidmat_b200_dds0_async(int nrows, int ncols, int nnz, const float *A, const float *B,
+                           const int *Cir, const int *Cjc, float *P, bidmat_stream_t stream) {
+    if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (nnz == 0 || ncols == 0) return 0;
+    if (!A || !B || !Cir || !Cjc || !P) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = as_stream(stream);
+    if (nrows == 0) return (int)cudaMemsetAsync(P, 0, (size_t)nnz * sizeof(float), st);
+    WorkspaceLease ws(pad256((size_t)nnz * 4) + 256, st);
+    if (ws.err != cudaSuccess) return (int)ws.err;
+    int *ic = ws.take<int>((size_t)nnz);
+    expand_jc_kernel<<<(unsigned)(((size_t)nnz + kThreads - 1) / kThreads), kThreads, 0, st>>>(ncols, nnz, Cjc, ic);
+    g_launches += 1;
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return (int)err;
+    return (int)launch_dds<false>(nrows, nnz, A, B, Cir, ic, P, st);
+}
+
+int bidmat_b200_dsmult(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                       const int *Bir, const int *Bic, float *C) {
+    if (nrows >= 0 && ncols >= 0 && (nnz == 0 || nrows == 0)) return 0;  // nothing to do, nothing to wait for
+    int e = bidmat_b200_dsmult_async(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, cudaStreamPerThread);
+    return finish_sync((cudaError_t)e, cudaStreamPerThread);
+}
+
+int bidmat_b200_dsmultT(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                        const int *Bir, const int *Bic, float *C) {
+    if (nrows >= 0 && ncols >= 0 && (nnz == 0 || nrows == 0)) return 0;
+    int e = bidmat_b200_dsmultT_async(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, 0, cudaStreamPerThread);
+    return finish_sync((cudaError_t)e, cudaStreamPerThread);
+}
+
+int bidmat_b200_dds(int nrows, int nnz, const float *A, const float *B, const int *Cir,
+                    const int *Cic, float *P) {
+    if (nrows >= 0 && nnz == 0) return 0;
+    int e = bidmat_b200_dds_async(nrows, nnz, A, B, Cir, Cic, P, cudaStreamPerThread);
+    return finish_sync((cudaError_t)e, cudaStreamPerThread);
+}
+
+int bidmat_b200_dds0(int nrows, int ncols, const float *A, const float *B, const int *Cir,
+                     const int *Cjc, float *P) {
+    if (nrows < 0 || ncols < 0) return (int)cudaErrorInvalidValue;
+    if (ncols == 0) return 0;
+    if (!Cjc) return (int)cudaErrorInvalidValue;
+    // nnz is not part of the reference signature: it is the last column pointer.
+    int nnz = 0;
+    cudaError_t err = cudaMemcpyAsync(&nnz, Cjc + ncols, sizeof(int), cudaMemcpyDeviceToHost, cudaStreamPerThread);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(cudaStreamPerThread);
+    if (err != cudaSuccess) return (int)err;
+    int e = bidmat_b200_dds0_async(nrows, ncols, nnz, A, B, Cir, Cjc, P, cudaStreamPerThread);
+    return finish_sync((cudaError_t)e, cudaStreamPerThread);
+}
+
+int bidmat_b200_dsmult_tune(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                            const int *Bir, const int *Bic, float *C, int, int) {
+    return bidmat_b200_dsmult(nrows, ncols, nnz, A, Bdata, Bir, Bic, C);
+}
+
+int bidmat_b200_dsmultx_tune(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                             const int *Bir, const int *Bic, float *C, int, int, int) {
+    return bidmat_b200_dsmult(nrows, ncols, nnz, A, Bdata, Bir, Bic, C);
+}
+
+int bidmat_b200_expand_jc(int ncols, int nnz, const int *jc, int *ic, bidmat_stream_t stream) {
+    if (ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (nnz == 0) return 0;
+    if (!jc || !ic || ncols == 0) return (int)cudaErrorInvalidValue;
+    expand_jc_kernel<<<(unsigned)(((size_t)nnz + kThreads - 1) / kThreads), kThreads, 0, as_stream(stream)>>>(ncols, nnz, jc, ic);
+    g_launches += 1;
+    return (int)cudaGetLastError();
+}
+
+int bidmat_b200_compress_ic(int ncols, int nnz, const int *ic, int *jc, bidmat_stream_t stream) {
+    if (ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (!jc || (nnz > 0 && !ic)) return (int)cudaErrorInvalidValue;
+    const size_t threads = nnz > 0 ? (size_t)nnz : (size_t)ncols + 1;
+    compress_ic_kernel<<<(unsigned)((threads + kThreads - 1) / kThreads), kThreads, 0, as_stream(stream)>>>(ncols, nnz, ic, jc);
+    g_launches += 1;
+    return (int)cudaGetLastError();
+}
+
+int bidmat_b200_check_structure(int m, int ncols, int nnz, const int *ir, const int *ic) {
+    if (m < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (nnz == 0) return 0;
+    if (!ir || !ic) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = cudaStreamPerThread;
+    WorkspaceLease ws(512, st);
+    if (ws.err != cudaSuccess) return (int)ws.err;
+    int *flags = ws.take<int>(1);
+    cudaError_t err = cudaMemsetAsync(flags, 0, sizeof(int), st);
+    if (err != cudaSuccess) return (int)err;
+    check_structure_kernel<<<(unsigned)(((size_t)nnz + kThreads - 1) / kThreads), kThreads, 0, st>>>(m, ncols, nnz, ir, ic, flags);
+    g_launches += 1;
+    int h = 0;
+    err = cudaMemcpyAsync(&h, flags, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+    if (err != cudaSuccess) return (int)err;
+    return h ? (int)cudaErrorInvalidValue : 0;
+}
+
+long long bidmat_b200_workspace_bytes(void) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+    std::lock_guard<std::mutex> g(g_ws[dev].mu);
+    return (long long)g_ws[dev].bytes;
+}
+
+int bidmat_b200_release_workspace(void) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return (int)err;
+    if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> g(g_ws[dev].mu);
+    if (g_ws[dev].ptr) {
+        err = cudaDeviceSynchronize();
+        cudaFree(g_ws[dev].ptr);
+        g_ws[dev].ptr = nullptr;
+        g_ws[dev].bytes = 0;
+    }
+    return (int)err;
+}
+
+long long bidmat_b200_launch_count(void) { return g_launches.load(); }
+
+int bidmat_b200_timing_enable(int on) {
+    g_timing.store(on ? 1 : 0);
+    return 0;
+}
+
+int bidmat_b200_timing_read(const char *label, double *total_ms, long long *count) {
+    if (!label || !total_ms || !count) return (int)cudaErrorInvalidValue;
+    std::lock_guard<std::mutex> g(g_span_mu);
+    double tot = 0.0;
+    long long c = 0;
+    for (const TimedSpan &sp : g_spans) {
+        if (strcmp(sp.label, label) != 0) continue;
+        cudaError_t err = cudaEventSynchronize(sp.b);
+        if (err != cudaSuccess) return (int)err;
+        float ms = 0.f;
+        err = cudaEventElapsedTime(&ms, sp.a, sp.b);
+        if (err != cudaSuccess) return (int)err;
+        tot += ms;
+        c++;
+    }
+    *total_ms = tot;
+    *count = c;
+    return 0;
+}
+
+int bidmat_b200_timing_reset(void) {
+    std::lock_guard<std::mutex> g(g_span_mu);
+    for (const TimedSpan &sp : g_spans) {
+        cudaEventDestroy(sp.a);
+        cudaEventDestroy(sp.b);
+    }
+    g_spans.clear();
+    return 0;
+}
+
+int bidmat_b200_version(void) { return 100; }
+
+const char *bidmat_b200_error_string(int err) { return cudaGetErrorString((cudaError_t)err); }
+
+}  // extern "C"

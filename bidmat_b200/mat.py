@@ -1,0 +1,330 @@
+"""Host-side mirror of BIDMat's operator interface for the sparse-dense path.
+
+BIDMat's host code is Scala and no JVM exists where this library is built, so
+the interface the Scala classes offer for this path is mirrored here with the
+same names, argument meaning and error behaviour, on top of the C ABI in
+include/bidmat_b200.h.  PyTorch only supplies device memory and streams.
+
+  SMat    CPU CSC sparse matrix      src/main/scala/BIDMat/SMat.scala, SparseMat.scala
+  GMat    dense fp32 device matrix   src/main/scala/BIDMat/GMat.scala
+  GSMat   sparse device matrix       src/main/scala/BIDMat/GSMat.scala
+  DDS     sampled dense-dense prod.  src/main/scala/BIDMat/MatFunctions.scala:1620-1674
+
+Indices are 0-based everywhere (BIDMat's CPU SMat is 1-based internally and is
+shifted on upload, GSMat.scala:626-628; the device layout is 0-based).
+"""
+import numpy as np
+import torch
+
+from . import _lib
+
+_L = _lib.lib
+
+
+class Mat:
+    """The few globals of BIDMat's `object Mat` that this path reads or writes
+    (src/main/scala/BIDMat/Mat.scala:670-724)."""
+    nflops = 0          # Mat.nflops: 2*k*nnz per product (GMat.scala:1057,1092; GSMat.scala:665)
+    debugStructure = False  # validate GSMat structure on the device before each native call
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _check(err, what):
+    if err != 0:
+        raise RuntimeError("%s %s" % (what, _lib.error_string(err)))
+
+
+class SMat:
+    """CPU sparse matrix in CSC form: jc (ncols+1), ir (nnz), data (nnz)."""
+
+    def __init__(self, nrows, ncols, jc, ir, data):
+        self.nrows = int(nrows)
+        self.ncols = int(ncols)
+        self.jc = np.ascontiguousarray(jc, dtype=np.int32)
+        self.ir = np.ascontiguousarray(ir, dtype=np.int32)
+        self.data = np.ascontiguousarray(data, dtype=np.float32)
+        if len(self.jc) != self.ncols + 1:
+            raise RuntimeError("jc should have ncols+1 entries")
+
+    @property
+    def nnz(self):
+        return int(self.jc[self.ncols])
+
+    def check(self):
+        """SparseMat.check (SparseMat.scala:710-740), 0-based."""
+        jc, ir = self.jc, self.ir
+        if jc[0] != 0:
+            raise RuntimeError("jc(0) should be 0")
+        if np.any(np.diff(jc) < 0):
+            raise RuntimeError("jc(i) out of order")
+        if jc[self.ncols] != len(ir):
+            raise RuntimeError("jc(ncols) should be %d" % len(ir))
+        if len(ir):
+            if ir.min() < 0:
+                raise RuntimeError("ir too small")
+            if ir.max() >= self.nrows:
+                raise RuntimeError("ir out of range")
+            ic = np.repeat(np.arange(self.ncols), np.diff(jc))
+            if np.any((np.diff(ir) <= 0) & (np.diff(ic) == 0)):
+                raise RuntimeError("ir(j) out of order")
+        return self
+
+    def full(self):
+        """Dense copy as a column-major (ncols, nrows) numpy array."""
+        out = np.zeros((self.ncols, self.nrows), dtype=np.float32)
+        ic = np.repeat(np.arange(self.ncols), np.diff(self.jc))
+        np.add.at(out, (ic, self.ir), self.data)
+        return out
+
+    @staticmethod
+    def from_scipy(S):
+        S = S.tocsc()
+        S.sort_indices()
+        return SMat(S.shape[0], S.shape[1], S.indptr, S.indices, S.data)
+
+
+class GMat:
+    """Dense fp32 matrix on the device, column-major nrows x ncols
+    (GMat.scala:20).  Backed by a contiguous torch tensor of shape
+    (ncols, nrows), so row i of the tensor is column i of the matrix."""
+
+    def __init__(self, tensor):
+        if tensor.dtype != torch.float32 or tensor.dim() != 2 or not tensor.is_contiguous():
+            raise RuntimeError("GMat needs a contiguous 2-D float32 tensor (ncols, nrows)")
+        if not tensor.is_cuda:
+            raise RuntimeError("GMat data must live on a CUDA device (no CPU fallback)")
+        self.t = tensor
+
+    @property
+    def nrows(self):
+        return int(self.t.shape[1])
+
+    @property
+    def ncols(self):
+        return int(self.t.shape[0])
+
+    @property
+    def pdata(self):
+        return self.t.data_ptr()
+
+    @staticmethod
+    def zeros(nrows, ncols, device=None):
+        return GMat(torch.zeros((ncols, nrows), dtype=torch.float32, device=device or "cuda"))
+
+    @staticmethod
+    def from_numpy(a, device=None):
+        """`a` is (ncols, nrows) C-contiguous = column-major nrows x ncols."""
+        return GMat(torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device or "cuda"))
+
+    def to_numpy(self):
+        return self.t.cpu().numpy()
+
+    def clear(self):
+        self.t.zero_()
+        return self
+
+    # ---- A * S ----------------------------------------------------------
+    def GSMult(self, a, oldmat=None):
+        """GMat.GSMult (GMat.scala:1041-1049): new or recycled zeroed output, then madd."""
+        a = GSMat.of(a, self.t.device)
+        if self.ncols != a.nrows:
+            raise RuntimeError("GSMult dimensions mismatch (%d %d) (%d %d)"
+                               % (self.nrows, self.ncols, a.nrows, a.ncols))
+        out = _new_or_check(self.nrows, a.ncols, oldmat, self.t.device)
+        out.clear()
+        return self.madd(a, out)
+
+    def madd(self, a, out):
+        """GMat.madd(SMat, FMat) (GMat.scala:1051-1074): out += this * a."""
+        a = GSMat.of(a, self.t.device)
+        if self.ncols != a.nrows or self.nrows != out.nrows or a.ncols != out.ncols:
+            raise RuntimeError("GSMadd dimensions mismatch (%d %d) (%d %d) (%d %d)"
+                               % (self.nrows, self.ncols, a.nrows, a.ncols, out.nrows, out.ncols))
+        Mat.nflops += 2 * self.nrows * a.nnz
+        a._debug_check()
+        err = _L.bidmat_b200_dsmult(self.nrows, a.ncols, a.nnz, self.pdata, _ptr(a.pdata),
+                                    _ptr(a.pir), _ptr(a.pic), out.pdata)
+        _check(err, "GMult: CUDA kernel error in CUMAT.dsmult")
+        return out
+
+    # ---- B *^ S ---------------------------------------------------------
+    def GSMultT(self, a, oldmat=None):
+        """GMat.GSMultT (GMat.scala:1076-1084)."""
+        a = GSMat.of(a, self.t.device)
+        if self.ncols != a.ncols:
+            raise RuntimeError("GSMult dimensions mismatch (%d %d) (%d %d)"
+                               % (self.nrows, self.ncols, a.ncols, a.nrows))
+        out = _new_or_check(self.nrows, a.nrows, oldmat, self.t.device)
+        out.clear()
+        return self.maddT(a, out)
+
+    def maddT(self, a, out):
+        """GMat.maddT (GMat.scala:1086-1096): out += this * a^T."""
+        a = GSMat.of(a, self.t.device)
+        if self.ncols != a.ncols or self.nrows != out.nrows or a.nrows != out.ncols:
+            raise RuntimeError("GSMadd dimensions mismatch (%d %d) (%d %d) (%d %d)"
+                               % (self.nrows, self.ncols, a.ncols, a.nrows, out.nrows, out.ncols))
+        Mat.nflops += 2 * self.nrows * a.nnz
+        a._debug_check()
+        err = _L.bidmat_b200_dsmultT(self.nrows, a.ncols, a.nnz, self.pdata, _ptr(a.pdata),
+                                     _ptr(a.pir), _ptr(a.pic), out.pdata)
+        _check(err, "GMult: CUDA kernel error in CUMAT.dsmultT")
+        return out
+
+    # ---- operators (GMat.scala:1684-1686, 1746-1748, 1972-1976) ----------
+    def __mul__(self, a):
+        """`A * S`."""
+        if isinstance(a, (GSMat, SMat)):
+            return self.GSMult(a, None)
+        return NotImplemented
+
+    def xT(self, a):
+        """`B *^ S` (also spelled xT in BIDMat)."""
+        return self.GSMultT(a, None)
+
+    def __matmul__(self, s):
+        """`B @@ S`: pairs a dense matrix with a sparsity pattern (GMat.scala:1972)."""
+        return GDSPair(self, s)
+
+    def Tx(self, pair):
+        """`A ^* (B @@ S)` = DDS(A, B, S) (GMat.scala:1973-1976)."""
+        if not isinstance(pair, GDSPair):
+            raise RuntimeError("^* on a GMat needs a (B @@ S) pair")
+        return DDS(self, pair.left, pair.right, None)
+
+
+class GDSPair:
+    """GDSPair (GMat.scala:1978-1990)."""
+
+    def __init__(self, left, right):
+        self.left = left
+        self.right = right
+
+
+def _new_or_check(nrows, ncols, oldmat, device):
+    """GMat.newOrCheckGMat without the GUID cache: reuse `oldmat` when it has the
+    right shape, else allocate."""
+    if oldmat is None:
+        return GMat(torch.empty((ncols, nrows), dtype=torch.float32, device=device))
+    if oldmat.nrows != nrows or oldmat.ncols != ncols:
+        raise RuntimeError("dimensions mismatch in output (%d %d) (%d %d)"
+                           % (oldmat.nrows, oldmat.ncols, nrows, ncols))
+    return oldmat
+
+
+class GSMat:
+    """Sparse matrix on the device in BIDMat's layout (GSMat.scala:14-15):
+    pir  int32 row per nonzero, pic int32 column per nonzero (non-decreasing),
+    pjc  int32 column pointers (ncols+1), pdata fp32 values."""
+
+    def __init__(self, nrows, ncols, nnz, pir, pic, pjc, pdata):
+        self.nrows = int(nrows)
+        self.ncols = int(ncols)
+        self.nnz = int(nnz)
+        self.pir, self.pic, self.pjc, self.pdata = pir, pic, pjc, pdata
+
+    @property
+    def device(self):
+        return self.pjc.device
+
+    @staticmethod
+    def of(a, device=None):
+        if isinstance(a, GSMat):
+            return a
+        if isinstance(a, SMat):
+            return GSMat.fromSMat(a, device)
+        raise RuntimeError("expected a GSMat or SMat")
+
+    @staticmethod
+    def fromSMat(a, device=None):
+        """GSMat.fromSMat (GSMat.scala:620-647): three uploads, then the column
+        pointers are expanded into per-nonzero columns on the device (the
+        reference calls cuSPARSE csr2coo for that step)."""
+        device = device or "cuda"
+        jc = torch.from_numpy(a.jc).to(device)
+        ir = torch.from_numpy(a.ir).to(device)
+        data = torch.from_numpy(a.data).to(device)
+        return GSMat.from_csc(a.nrows, a.ncols, jc, ir, data)
+
+    @staticmethod
+    def from_csc(nrows, ncols, jc, ir, data):
+        """Build from device tensors jc/ir/data, deriving pic on the device."""
+        nnz = int(ir.numel())
+        ic = torch.empty(nnz, dtype=torch.int32, device=ir.device)
+        if nnz:
+            with torch.cuda.device(ir.device):
+                err = _L.bidmat_b200_expand_jc(ncols, nnz, jc.data_ptr(), ic.data_ptr(),
+                                               torch.cuda.current_stream().cuda_stream)
+                _check(err, "Cuda error in GSMAT.fromSMat")
+        return GSMat(nrows, ncols, nnz, ir, ic, jc, data)
+
+    def toSMat(self):
+        """GSMat.toSMat (GSMat.scala:108-127): jc is rebuilt from pic."""
+        ic = self.pic.cpu().numpy()
+        jc = np.zeros(self.ncols + 1, dtype=np.int32)
+        np.cumsum(np.bincount(ic, minlength=self.ncols), out=jc[1:])
+        return SMat(self.nrows, self.ncols, jc, self.pir.cpu().numpy(), self.pdata.cpu().numpy())
+
+    def colslice(self, col1, col2):
+        """GSMat.colslice (GSMat.scala:77-104): columns [col1, col2) with local,
+        zero-based column indices and re-based column pointers."""
+        j0 = int(self.pjc[col1])
+        j1 = int(self.pjc[col2])
+        return GSMat(self.nrows, col2 - col1, j1 - j0, self.pir[j0:j1].clone(),
+                     (self.pic[j0:j1] - col1).to(torch.int32), (self.pjc[col1:col2 + 1] - j0).to(torch.int32),
+                     self.pdata[j0:j1].clone())
+
+    def _debug_check(self):
+        if Mat.debugStructure and self.nnz:
+            err = _L.bidmat_b200_check_structure(self.nrows, self.ncols, self.nnz, _ptr(self.pir), _ptr(self.pic))
+            _check(err, "GSMat structure check failed:")
+
+    def _like(self, oldmat):
+        if oldmat is not None:
+            if oldmat.nrows != self.nrows or oldmat.ncols != self.ncols or oldmat.nnz != self.nnz:
+                raise RuntimeError("dimensions mismatch in output GSMat")
+            return oldmat
+        return GSMat(self.nrows, self.ncols, self.nnz, torch.empty_like(self.pir), torch.empty_like(self.pic),
+                     self.pjc.clone(), torch.empty_like(self.pdata))
+
+    @staticmethod
+    def DDS(A, B, C, oldmat=None):
+        """GSMat.DDS (GSMat.scala:649-667): copy C's row and column indices into
+        the output, clear its values, accumulate the sampled products."""
+        if A.nrows != B.nrows or C.nrows != A.ncols or C.ncols != B.ncols:
+            raise RuntimeError("dimensions mismatch %d,%d  %d,%d  %d,%d"
+                               % (A.nrows, A.ncols, B.nrows, B.ncols, C.nrows, C.ncols))
+        out = C._like(oldmat)
+        out.pir.copy_(C.pir)
+        out.pic.copy_(C.pic)
+        out.pdata.zero_()
+        C._debug_check()
+        err = _L.bidmat_b200_dds(A.nrows, C.nnz, A.pdata, B.pdata, _ptr(C.pir), _ptr(C.pic), _ptr(out.pdata))
+        _check(err, "DDS kernel error")
+        Mat.nflops += 2 * C.nnz * A.nrows
+        return out
+
+    @staticmethod
+    def DDS0(A, B, C, oldmat=None):
+        """GSMat.DDS0 (GSMat.scala:669-684): the column-pointer driven form."""
+        if A.nrows != B.nrows or C.nrows != A.ncols or C.ncols != B.ncols:
+            raise RuntimeError("dimensions mismatch")
+        out = C._like(oldmat)
+        out.pir.copy_(C.pir)
+        out.pic.copy_(C.pic)
+        out.pdata.zero_()
+        err = _L.bidmat_b200_dds0(A.nrows, C.ncols, A.pdata, B.pdata, _ptr(C.pir), _ptr(C.pjc), _ptr(out.pdata))
+        _check(err, "DDS kernel error")
+        Mat.nflops += 2 * C.nnz * A.nrows
+        return out
+
+
+def DDS(A, B, C, omat=None):
+    """MatFunctions.DDS (MatFunctions.scala:1620-1674) for (GMat, GMat, GSMat):
+    P = C's pattern sampled from A^T * B."""
+    if isinstance(A, GMat) and isinstance(B, GMat) and isinstance(C, (GSMat, SMat)):
+        return GSMat.DDS(A, B, GSMat.of(C, A.t.device), omat)
+    raise RuntimeError("DDS: unsupported operand types (device operands only; no CPU fallback)")

@@ -1,0 +1,84 @@
+"""One rank's share of the sparse-dense path, on device-resident operands.
+
+The sparse matrix is split by contiguous column ranges of (nearly) equal
+nonzero count; the dense model A (k x m) is replicated; B, C and P follow the
+columns.  A*S and DDS need no communication; the k x m result of B*^S is a
+partial sum per rank and is summed over ranks with one allreduce
+(the composition BIDMat leaves to its caller: GFunctions.ncclAllReduce,
+src/main/scala/BIDMat/GFunctions.scala:175-203).
+
+Shards carry local, zero-based column indices, as GSMat.colslice produces
+(src/main/scala/BIDMat/GSMat.scala:77-104).
+"""
+import torch
+
+from . import _lib
+from .gen import shard_columns
+
+_L = _lib.lib
+
+
+def _ck(err, what):
+    if err != 0:
+        raise RuntimeError("%s: %s" % (what, _lib.error_string(err)))
+
+
+class ColumnShard:
+    """Device tensors of one column range of a CSC matrix."""
+
+    def __init__(self, m, jc, ir, data, col0, col1):
+        j0, j1 = int(jc[col0]), int(jc[col1])
+        self.m = int(m)
+        self.col0, self.col1 = int(col0), int(col1)
+        self.n = self.col1 - self.col0
+        self.nnz = j1 - j0
+        self.jc = (jc[col0:col1 + 1] - j0).to(torch.int32).contiguous()
+        self.ir = ir[j0:j1].contiguous()
+        self.data = data[j0:j1].contiguous()
+        self.ic = torch.empty(self.nnz, dtype=torch.int32, device=ir.device)
+        if self.nnz:
+            _ck(_L.bidmat_b200_expand_jc(self.n, self.nnz, self.jc.data_ptr(), self.ic.data_ptr(),
+                                         torch.cuda.current_stream().cuda_stream), "expand_jc")
+
+
+def make_shard(problem, rank, world):
+    bounds = shard_columns(problem.jc, world)
+    return ColumnShard(problem.m, problem.jc, problem.ir, problem.data, bounds[rank], bounds[rank + 1]), bounds
+
+
+class PathStep:
+    """A*S, DDS(A,B,S) and B*^S (+ allreduce) on one rank's shard, enqueued on
+    one stream through the stream-ordered C ABI."""
+
+    def __init__(self, k, shard, A, B_local, stream, group=None):
+        self.k, self.S, self.A, self.B, self.stream, self.group = int(k), shard, A, B_local, stream, group
+        dev = A.device
+        self.C = torch.zeros((shard.n, k), dtype=torch.float32, device=dev)
+        self.P = torch.zeros(shard.nnz, dtype=torch.float32, device=dev)
+        self.G = torch.zeros((shard.m, k), dtype=torch.float32, device=dev)
+
+    def dsmult(self):
+        S = self.S
+        self.C.zero_()   # GMat.GSMult clears the output before the native call (GMat.scala:1047)
+        _ck(_L.bidmat_b200_dsmult_async(self.k, S.n, S.nnz, self.A.data_ptr(), S.data.data_ptr(), S.ir.data_ptr(),
+                                        S.ic.data_ptr(), self.C.data_ptr(), self.stream.cuda_stream), "dsmult")
+
+    def dds(self):
+        S = self.S
+        self.P.zero_()   # GSMat.DDS clears the values first (GSMat.scala:662)
+        _ck(_L.bidmat_b200_dds_async(self.k, S.nnz, self.A.data_ptr(), self.B.data_ptr(), S.ir.data_ptr(),
+                                     S.ic.data_ptr(), self.P.data_ptr(), self.stream.cuda_stream), "dds")
+
+    def dsmultT(self):
+        S = self.S
+        self.G.zero_()   # GMat.GSMultT clears the output (GMat.scala:1082)
+        _ck(_L.bidmat_b200_dsmultT_async(self.k, S.n, S.nnz, self.B.data_ptr(), S.data.data_ptr(), S.ir.data_ptr(),
+                                         S.ic.data_ptr(), self.G.data_ptr(), S.m, self.stream.cuda_stream), "dsmultT")
+        if self.group is not None:
+            import torch.distributed as dist
+            dist.all_reduce(self.G, op=dist.ReduceOp.SUM, group=self.group)
+
+    def run(self):
+        self.dsmult()
+        self.dds()
+        self.dsmultT()

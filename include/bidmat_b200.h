@@ -1,0 +1,145 @@
+/*
+ * bidmat_b200.h -- C ABI of the B200 (sm_100a) sparse-dense library.
+ *
+ * This is the drop-in boundary for BIDMat's native calls on one path: the
+ * dense x sparse products behind GMat*GSMat and GMat*^GSMat and the sampled
+ * dense-dense product DDS.  Every function takes plain device pointers and
+ * sizes, returns a cudaError_t cast to int (0 = success) and never aborts the
+ * process.  Conventions shared by all entry points:
+ *
+ *   - dense matrices are column-major fp32 with leading dimension nrows (k):
+ *     column c starts at base + c*nrows  (BIDMat GMat.pdata layout,
+ *     src/main/scala/BIDMat/GMat.scala:20);
+ *   - a sparse matrix is BIDMat's GSMat device layout
+ *     (src/main/scala/BIDMat/GSMat.scala:14-15): int32 0-based row index per
+ *     nonzero (pir), int32 0-based column index per nonzero in non-decreasing
+ *     order (pic), fp32 value per nonzero (pdata), and int32 column pointers
+ *     (pjc, ncols+1 entries) where a function says so;
+ *   - rows inside a column may be unsorted or repeated; empty columns are fine;
+ *   - all pointers are owned by the caller and live on the calling thread's
+ *     current device; only the output array is written;
+ *   - nnz == 0 is a successful no-op.
+ *
+ * The four functions without suffix are synchronous on the per-thread default
+ * stream, exactly like the launchers they replace.  The *_async variants
+ * enqueue on a caller-supplied stream and return without synchronising.
+ * Scratch memory, where an operation needs it, comes from a per-device
+ * workspace owned by the library (grown on demand, reused across calls,
+ * released by bidmat_b200_release_workspace).
+ */
+#ifndef BIDMAT_B200_H
+#define BIDMAT_B200_H
+
+#if defined(__GNUC__)
+#define BIDMAT_B200_API __attribute__((visibility("default")))
+#else
+#define BIDMAT_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque stream handle: a cudaStream_t passed as void* so that this header
+ * needs no CUDA include. NULL selects the per-thread default stream. */
+typedef void *bidmat_stream_t;
+
+/* C(nrows x ncols) += A(nrows x m) * S(m x ncols).
+ * Replaces: int dsmult(int,int,int,float*,float*,int*,int*,float*)
+ *   jni/include/MatKernel.hpp:140, jni/src/Arith.cu:46-60, bound from
+ *   CUMAT.dsmult (src/main/java/edu/berkeley/bid/CUMAT.java:143) through
+ *   Java_edu_berkeley_bid_CUMAT_dsmult (jni/src/BIDMat_CUMAT.cpp:722-733). */
+BIDMAT_B200_API int bidmat_b200_dsmult(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                       const int *Bir, const int *Bic, float *C);
+
+/* C(nrows x m) += A(nrows x ncols) * S(m x ncols)^T.  m is not passed by the
+ * reference interface; the rows written are exactly those named in Bir.
+ * Replaces: int dsmultT(...) jni/include/MatKernel.hpp:150,
+ *   jni/src/Arith.cu:234-248, CUMAT.dsmultT (CUMAT.java:152),
+ *   Java_edu_berkeley_bid_CUMAT_dsmultT (BIDMat_CUMAT.cpp:761-772). */
+BIDMAT_B200_API int bidmat_b200_dsmultT(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                        const int *Bir, const int *Bic, float *C);
+
+/* P[j] += <A[:, Cir[j]], B[:, Cic[j]]> for j in [0, nnz).
+ * Replaces: int dds(int,int,float*,float*,int*,int*,float*)
+ *   jni/include/MatKernel.hpp:154, jni/src/Arith.cu:381-389, CUMAT.dds
+ *   (CUMAT.java:211), Java_edu_berkeley_bid_CUMAT_dds
+ *   (BIDMat_CUMAT.cpp:774-785). */
+BIDMAT_B200_API int bidmat_b200_dds(int nrows, int nnz, const float *A, const float *B, const int *Cir,
+                    const int *Cic, float *P);
+
+/* P[j] = <A[:, Cir[j]], B[:, c]> for j in [Cjc[c], Cjc[c+1]), c in [0, ncols):
+ * the column-pointer driven form, which stores instead of accumulating.
+ * Valid for any nrows (the reference kernel is only meaningful for 1024).
+ * Replaces: int dds0(int,int,float*,float*,int*,int*,float*)
+ *   jni/include/MatKernel.hpp:156, jni/src/Arith.cu:391-399, CUMAT.dds0
+ *   (CUMAT.java:213), Java_edu_berkeley_bid_CUMAT_dds0
+ *   (BIDMat_CUMAT.cpp:787-798). */
+BIDMAT_B200_API int bidmat_b200_dds0(int nrows, int ncols, const float *A, const float *B, const int *Cir,
+                     const int *Cjc, float *P);
+
+/* Launch-shape tuning hooks of the reference: same result as dsmult; the
+ * shape arguments are accepted and ignored.
+ * Replaces: dsmult_tune / dsmultx_tune (jni/include/MatKernel.hpp:146-148,
+ *   jni/src/Arith.cu:191-204, CUMAT.java:148-150, BIDMat_CUMAT.cpp:735-759). */
+BIDMAT_B200_API int bidmat_b200_dsmult_tune(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                            const int *Bir, const int *Bic, float *C, int nblocks, int nthreads);
+BIDMAT_B200_API int bidmat_b200_dsmultx_tune(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                             const int *Bir, const int *Bic, float *C, int nblocks, int nthreadsx,
+                             int nthreadsy);
+
+/* Stream-ordered forms of the four operations.  They enqueue on `stream` and do
+ * not wait.  dsmultT_async takes the row count m of S as a hint (<= 0 when
+ * unknown: the library then finds the largest row index itself, which costs a
+ * host round trip inside the call). */
+BIDMAT_B200_API int bidmat_b200_dsmult_async(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                             const int *Bir, const int *Bic, float *C, bidmat_stream_t stream);
+BIDMAT_B200_API int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                              const int *Bir, const int *Bic, float *C, int m_hint,
+                              bidmat_stream_t stream);
+BIDMAT_B200_API int bidmat_b200_dds_async(int nrows, int nnz, const float *A, const float *B, const int *Cir,
+                          const int *Cic, float *P, bidmat_stream_t stream);
+BIDMAT_B200_API int bidmat_b200_dds0_async(int nrows, int ncols, int nnz, const float *A, const float *B,
+                           const int *Cir, const int *Cjc, float *P, bidmat_stream_t stream);
+
+/* Structure helpers on the device (the steps BIDMat performs around the path
+ * with cuSPARSE csr2coo and a host loop: GSMat.fromSMat, GSMat.scala:639, and
+ * SparseMat.compressInds, SparseMat.scala:857-868).
+ *   expand:   ic[j] = c for j in [jc[c], jc[c+1])
+ *   compress: jc[c] = number of nonzeros with ic < c, c in [0, ncols] */
+BIDMAT_B200_API int bidmat_b200_expand_jc(int ncols, int nnz, const int *jc, int *ic, bidmat_stream_t stream);
+BIDMAT_B200_API int bidmat_b200_compress_ic(int ncols, int nnz, const int *ic, int *jc, bidmat_stream_t stream);
+
+/* Validates a GSMat structure on the device without touching values:
+ * 0 <= ir < m, 0 <= ic < ncols, ic non-decreasing.  Returns 0 when it holds,
+ * cudaErrorInvalidValue (1) when it does not, another cudaError_t on failure.
+ * Synchronous. */
+BIDMAT_B200_API int bidmat_b200_check_structure(int m, int ncols, int nnz, const int *ir, const int *ic);
+
+/* Bytes currently held by the calling thread's device workspace, and its
+ * release (frees the device memory; the next call grows it again). */
+BIDMAT_B200_API long long bidmat_b200_workspace_bytes(void);
+BIDMAT_B200_API int bidmat_b200_release_workspace(void);
+
+/* Number of kernels this library has launched in this process (all devices);
+ * the benchmark reports the difference across its timed region. */
+BIDMAT_B200_API long long bidmat_b200_launch_count(void);
+
+/* Optional per-kernel timing for benchmarks.  While enabled, the launchers
+ * bracket their main kernels with CUDA events on the launching stream.
+ * timing_read sums the spans recorded under `label` ("dsmult_ga_chunk",
+ * "dsmultT_ga_chunk", "dsmultT_rowsort", "ga_fixup", "dds_chunk") after waiting
+ * for them; timing_reset discards all spans.  All spans must belong to the
+ * calling thread's current device. */
+BIDMAT_B200_API int bidmat_b200_timing_enable(int on);
+BIDMAT_B200_API int bidmat_b200_timing_read(const char *label, double *total_ms, long long *count);
+BIDMAT_B200_API int bidmat_b200_timing_reset(void);
+
+/* Library version, and the text of a cudaError_t for error messages. */
+BIDMAT_B200_API int bidmat_b200_version(void);
+BIDMAT_B200_API const char *bidmat_b200_error_string(int err);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BIDMAT_B200_H */

@@ -1,0 +1,241 @@
+"""ctypes front end of the CPU checker (TEST INFRASTRUCTURE, not product code).
+
+Conventions: dense matrices are numpy float32 arrays of shape (ncols, k), C
+contiguous, which is BIDMat's column-major k x ncols layout
+(src/main/scala/BIDMat/FMat.scala data array); S is CSC with 0-based int32
+``jc`` (n+1), ``ir`` (nnz) and float32 ``data`` (nnz).
+
+dsmult / dsmultT ACCUMULATE into the array passed as ``out`` (FMat.madd /
+FMat.maddT semantics, FMat.scala:1167, 1410); when ``out`` is None a zeroed
+array is used, which is what ``A * S`` and ``B *^ S`` do (FMat.scala:1162,
+1405).  dds STORES (MatFunctions.scala:1612).
+"""
+import ctypes
+import os
+
+import numpy as np
+
+from . import build as _build
+
+_F32P = ctypes.POINTER(ctypes.c_float)
+_F64P = ctypes.POINTER(ctypes.c_double)
+_I32P = ctypes.POINTER(ctypes.c_int32)
+
+_lib = None
+_ref = None
+_ref_tried = False
+
+
+def _load():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(_build.build_oracle())
+        for name in ("oracle_dsmult", "oracle_dsmultT"):
+            getattr(_lib, name).argtypes = [ctypes.c_int, ctypes.c_int, _F32P, _F32P, _I32P, _I32P,
+                                            _F32P, ctypes.c_int]
+            getattr(_lib, name).restype = None
+        _lib.oracle_dds.argtypes = [ctypes.c_int, ctypes.c_int, _F32P, _F32P, _I32P, _I32P, _F32P,
+                                    ctypes.c_int]
+        _lib.oracle_dds.restype = None
+        for name in ("oracle_dsmult_f64", "oracle_dsmultT_f64"):
+            getattr(_lib, name).argtypes = [ctypes.c_int, ctypes.c_int, _F32P, _F32P, _I32P, _I32P,
+                                            _F64P, _F64P, ctypes.c_int]
+            getattr(_lib, name).restype = None
+        _lib.oracle_dds_f64.argtypes = [ctypes.c_int, ctypes.c_int, _F32P, _F32P, _I32P, _I32P,
+                                        _F64P, _F64P, ctypes.c_int]
+        _lib.oracle_dds_f64.restype = None
+        _lib.oracle_uncompress_inds.argtypes = [_I32P, ctypes.c_int, _I32P]
+        _lib.oracle_uncompress_inds.restype = None
+        _lib.oracle_compress_inds.argtypes = [_I32P, ctypes.c_int, ctypes.c_int32, _I32P]
+        _lib.oracle_compress_inds.restype = None
+        _lib.oracle_check_csc.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int32, _I32P, _I32P]
+        _lib.oracle_check_csc.restype = ctypes.c_int
+    return _lib
+
+
+def _load_ref():
+    global _ref, _ref_tried
+    if not _ref_tried:
+        _ref_tried = True
+        path = _build.build_reference()
+        if path and os.path.exists(path):
+            _ref = ctypes.CDLL(path)
+            for name in ("ref_smcscm", "ref_smcsrm"):
+                getattr(_ref, name).argtypes = [ctypes.c_int, ctypes.c_int, _F32P, _F32P, _I32P,
+                                                _I32P, _F32P]
+                getattr(_ref, name).restype = None
+    return _ref
+
+
+def default_threads():
+    return os.cpu_count() or 1
+
+
+def _f32(a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return a, a.ctypes.data_as(_F32P)
+
+
+def _i32(a):
+    a = np.ascontiguousarray(a, dtype=np.int32)
+    return a, a.ctypes.data_as(_I32P)
+
+
+def _dense_k(a):
+    if a.ndim != 2:
+        raise ValueError("dense operand must be 2-D (ncols, k)")
+    return int(a.shape[1])
+
+
+def dsmult(A, data, ir, jc, out=None, nthreads=None):
+    """C(k x n) += A(k x m) * S.  FMat.fSMultHelper order."""
+    A, pA = _f32(A)
+    k = _dense_k(A)
+    data, pd = _f32(data)
+    ir, pir = _i32(ir)
+    jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    if out is None:
+        out = np.zeros((n, k), dtype=np.float32)
+    assert out.dtype == np.float32 and out.flags.c_contiguous and out.shape == (n, k)
+    _load().oracle_dsmult(k, n, pA, pd, pir, pjc, out.ctypes.data_as(_F32P),
+                          nthreads or default_threads())
+    return out
+
+
+def dsmultT(B, data, ir, jc, m, out=None, nthreads=None):
+    """C(k x m) += B(k x n) * S^T.  FMat.fSMultTHelper2 order."""
+    B, pB = _f32(B)
+    k = _dense_k(B)
+    data, pd = _f32(data)
+    ir, pir = _i32(ir)
+    jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    assert B.shape[0] == n
+    if out is None:
+        out = np.zeros((m, k), dtype=np.float32)
+    assert out.dtype == np.float32 and out.flags.c_contiguous and out.shape == (m, k)
+    _load().oracle_dsmultT(k, n, pB, pd, pir, pjc, out.ctypes.data_as(_F32P),
+                           nthreads or default_threads())
+    return out
+
+
+def dds(A, B, ir, jc, nthreads=None):
+    """P.data[j] = <A[:, ir[j]], B[:, col(j)]>.  MatFunctions.DDShelper order."""
+    A, pA = _f32(A)
+    B, pB = _f32(B)
+    k = _dense_k(A)
+    assert _dense_k(B) == k
+    ir, pir = _i32(ir)
+    jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    out = np.zeros(len(ir), dtype=np.float32)
+    _load().oracle_dds(k, n, pA, pB, pir, pjc, out.ctypes.data_as(_F32P),
+                       nthreads or default_threads())
+    return out
+
+
+def dsmult_f64(A, data, ir, jc, nthreads=None):
+    """fp64 value and sum|term| of A*S."""
+    A, pA = _f32(A)
+    k = _dense_k(A)
+    data, pd = _f32(data)
+    ir, pir = _i32(ir)
+    jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    out = np.zeros((n, k), dtype=np.float64)
+    oab = np.zeros((n, k), dtype=np.float64)
+    _load().oracle_dsmult_f64(k, n, pA, pd, pir, pjc, out.ctypes.data_as(_F64P),
+                              oab.ctypes.data_as(_F64P), nthreads or default_threads())
+    return out, oab
+
+
+def dsmultT_f64(B, data, ir, jc, m, nthreads=None):
+    """fp64 value and sum|term| of B*^S."""
+    B, pB = _f32(B)
+    k = _dense_k(B)
+    data, pd = _f32(data)
+    ir, pir = _i32(ir)
+    jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    out = np.zeros((m, k), dtype=np.float64)
+    oab = np.zeros((m, k), dtype=np.float64)
+    _load().oracle_dsmultT_f64(k, n, pB, pd, pir, pjc, out.ctypes.data_as(_F64P),
+                               oab.ctypes.data_as(_F64P), nthreads or default_threads())
+    return out, oab
+
+
+def dds_f64(A, B, ir, jc, nthreads=None):
+    """fp64 value and sum|term| of DDS."""
+    A, pA = _f32(A)
+    B, pB = _f32(B)
+    k = _dense_k(A)
+    ir, pir = _i32(ir)
+    jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    out = np.zeros(len(ir), dtype=np.float64)
+    oab = np.zeros(len(ir), dtype=np.float64)
+    _load().oracle_dds_f64(k, n, pA, pB, pir, pjc, out.ctypes.data_as(_F64P),
+                           oab.ctypes.data_as(_F64P), nthreads or default_threads())
+    return out, oab
+
+
+def uncompress_inds(jc):
+    jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    ic = np.empty(int(jc[n]), dtype=np.int32)
+    _load().oracle_uncompress_inds(pjc, n, ic.ctypes.data_as(_I32P))
+    return ic
+
+
+def compress_inds(ic, n):
+    ic, pic = _i32(ic)
+    jc = np.empty(n + 1, dtype=np.int32)
+    _load().oracle_compress_inds(pic, n, len(ic), jc.ctypes.data_as(_I32P))
+    return jc
+
+
+def check_csc(m, n, ir, jc):
+    ir, pir = _i32(ir)
+    jc, pjc = _i32(jc)
+    return _load().oracle_check_csc(m, n, len(ir), pir, pjc)
+
+
+def ref_available():
+    return _load_ref() is not None
+
+
+def ref_smcscm(A, data, ir, jc, out=None):
+    """The reference's own compiled loop for A*S (BIDMat_SPBLAS.c:364-395).
+    Uses OpenMP's default thread count over columns, as the reference does."""
+    lib = _load_ref()
+    if lib is None:
+        raise RuntimeError("reference build oracle/_ref/libspblas_ref.so is not available")
+    A, pA = _f32(A)
+    k = _dense_k(A)
+    data, pd = _f32(data)
+    ir, pir = _i32(ir)
+    jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    if out is None:
+        out = np.zeros((n, k), dtype=np.float32)
+    lib.ref_smcscm(k, n, pA, pd, pir, pjc, out.ctypes.data_as(_F32P))
+    return out
+
+
+def ref_smcsrm(B, data, ir, jc, m, out=None):
+    """The reference's own compiled loop for B*^S (BIDMat_SPBLAS.c:397-427);
+    single-threaded, as in the reference."""
+    lib = _load_ref()
+    if lib is None:
+        raise RuntimeError("reference build oracle/_ref/libspblas_ref.so is not available")
+    B, pB = _f32(B)
+    k = _dense_k(B)
+    data, pd = _f32(data)
+    ir, pir = _i32(ir)
+    jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    if out is None:
+        out = np.zeros((m, k), dtype=np.float32)
+    lib.ref_smcsrm(k, n, pB, pd, pir, pjc, out.ctypes.data_as(_F32P))
+    return out
