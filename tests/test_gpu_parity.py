@@ -245,7 +245,7 @@ def test_mirror_operators_and_errors(cuda_device):
     with pytest.raises(RuntimeError, match="GSMult dimensions mismatch"):
         bb.xT(aa)
     with pytest.raises(RuntimeError, match="dimensions mismatch"):
-        GSMat.DDS(bb, ee, aa)
+        GSMat.DDS(ee, bb, aa)        # A would need as many columns as S has rows
     # ^* with a (B @@ S) pair
     A = GMat.from_numpy(rng.standard_normal((nk, 16)).astype(np.float32), cuda_device)
     B = GMat.from_numpy(rng.standard_normal((nc, 16)).astype(np.float32), cuda_device)
