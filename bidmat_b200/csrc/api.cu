@@ -15,12 +15,13 @@
 
 #include "../../include/bidmat_b200.h"
 #include "kernels.cuh"
+#include "structure_kernels.cuh"
+#include "host_common.cuh"
 
 using namespace bidmat;
 
 namespace {
 
-std::atomic<long long> g_launches{0};
 
 // ------------------------------------------------------------------ timing
 // Optional per-kernel timing for the benchmark: when enabled, the launchers
@@ -111,76 +112,6 @@ struct WorkspaceLease {
 
 inline size_t pad256(size_t b) { return (b + 255) & ~size_t(255); }
 
-// ------------------------------------------------------------------ shapes
-// How a dense column of height k is spread over a worker.
-struct Shape {
-    int vec;   // 4 when k % 4 == 0 and the pointers are 16-byte aligned, else 1
-    int lpv;   // lanes per worker
-    int nt;    // VEC-wide elements per lane
-    int tiles; // k-tiles of width lpv*nt*vec
-};
-
-Shape pick_shape(int k, bool aligned16) {
-    Shape s;
-    s.vec = (aligned16 && (k % 4 == 0)) ? 4 : 1;
-    const int kv = k / s.vec;
-    if (kv <= 8) { s.lpv = 8; s.nt = 1; }
-    else if (kv <= 16) { s.lpv = 16; s.nt = 1; }
-    else if (kv <= 32) { s.lpv = 32; s.nt = 1; }
-    else if (kv <= 64) { s.lpv = 32; s.nt = 2; }
-    else { s.lpv = 32; s.nt = 4; }
-    const int tile = s.lpv * s.nt * s.vec;
-    s.tiles = (k + tile - 1) / tile;
-    return s;
-}
-
-bool is16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
-
-int env_int(const char *name, int dflt) {
-    const char *v = getenv(name);
-    if (!v || !*v) return dflt;
-    return atoi(v);
-}
-
-// Chunk length: aim at about 64K chunks so that the hardware scheduler can
-// balance them over 148 SMs, but never fewer than 64 nor more than 4096
-// nonzeros per chunk.  BIDMAT_B200_CHUNK overrides (tests use tiny chunks to
-// force runs across chunk boundaries).
-int pick_chunk(long long nnz, int lpv) {
-    int forced = env_int("BIDMAT_B200_CHUNK", 0);
-    long long c;
-    if (forced > 0) c = forced;
-    else {
-        c = (nnz + 65535) / 65536;
-        if (c < 64) c = 64;
-        if (c > 4096) c = 4096;
-    }
-    c = ((c + lpv - 1) / lpv) * lpv;
-    return (int)c;
-}
-
-#define DISPATCH_SHAPE(S, CALL)                                                     \
-    do {                                                                            \
-        if ((S).vec == 4) {                                                         \
-            if ((S).lpv == 8) { CALL(4, 8, 1); }                                    \
-            else if ((S).lpv == 16) { CALL(4, 16, 1); }                             \
-            else if ((S).nt == 1) { CALL(4, 32, 1); }                               \
-            else if ((S).nt == 2) { CALL(4, 32, 2); }                               \
-            else { CALL(4, 32, 4); }                                                \
-        } else {                                                                    \
-            if ((S).lpv == 8) { CALL(1, 8, 1); }                                    \
-            else if ((S).lpv == 16) { CALL(1, 16, 1); }                             \
-            else if ((S).nt == 1) { CALL(1, 32, 1); }                               \
-            else if ((S).nt == 2) { CALL(1, 32, 2); }                               \
-            else { CALL(1, 32, 4); }                                                \
-        }                                                                           \
-    } while (0)
-
-unsigned blocks_for(long long workers, int lpv) {
-    long long threads = workers * lpv;
-    return (unsigned)((threads + kThreads - 1) / kThreads);
-}
-
 // O[:, seg[j]] += val[j] * D[:, gidx[j]] with `part` holding 2*nchunks*k floats.
 cudaError_t launch_ga(int k, long long nnz, const float *D, const float *val, const int *gidx,
                       const int *seg, float *O, float *part, int chunk, const Shape &s,
@@ -201,11 +132,6 @@ cudaError_t launch_ga(int k, long long nnz, const float *D, const float *val, co
 #undef CALL_GA
     g_launches += (nchunks > 1) ? 2 : 1;
     return cudaGetLastError();
-}
-
-size_t ga_part_floats(int k, long long nnz, int chunk) {
-    const long long nchunks = (nnz + chunk - 1) / chunk;
-    return (size_t)nchunks * 2 * (size_t)k;
 }
 
 template <bool ACCUM>
