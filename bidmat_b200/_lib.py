@@ -24,6 +24,7 @@ _SIGNATURES = {
     "bidmat_b200_dsmultx_tune": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),
     "bidmat_b200_dsmult_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dsmultT_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _c_int, _vp]),
+    "bidmat_b200_dsmult_noalloc": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dds_async": (_c_int, [_c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dds0_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_expand_jc": (_c_int, [_c_int, _c_int, _vp, _vp, _vp]),

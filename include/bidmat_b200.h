@@ -102,6 +102,35 @@ BIDMAT_B200_API int bidmat_b200_dds_async(int nrows, int nnz, const float *A, co
 BIDMAT_B200_API int bidmat_b200_dds0_async(int nrows, int ncols, int nnz, const float *A, const float *B,
                            const int *Cir, const int *Cjc, float *P, bidmat_stream_t stream);
 
+/* A*S without any allocation.  No counterpart in the reference: BIDMat's
+ * launchers never needed scratch memory.  It exists for callers that cannot let a
+ * library allocate on the device: host applications that have handed all device
+ * memory to their own caching allocator (BIDMat's GPU cache, a full PyTorch pool),
+ * where a cudaMalloc from inside this library may fail or fragment that pool, and
+ * multi-stream serving loops that cannot afford the device-wide synchronisation
+ * cudaMalloc/cudaFree imply.
+ *
+ * Same result and same stream-ordered behaviour as bidmat_b200_dsmult_async (the
+ * sums of columns split over different chunk boundaries may differ in the last
+ * bits).  The scratch is a fixed array of BIDMAT_B200_NOALLOC_SCRATCH_FLOATS
+ * floats (16 MiB) that every GPU loading the library holds until exit.
+ *   Limit: 2*nrows*ceil(nnz/chunk) floats must fit the array for some chunk
+ *   length <= BIDMAT_B200_NOALLOC_MAX_CHUNK, i.e.
+ *       nnz <= BIDMAT_B200_NOALLOC_MAX_CHUNK * floor(SCRATCH_FLOATS / (2*nrows))
+ *   (134,217,728 nonzeros at nrows = 256).  Larger problems are rejected with
+ *   cudaErrorInvalidValue before anything is launched; use dsmult_async then.
+ *   First call on a device: resolves the array's device address with
+ *   cudaGetSymbolAddress.  Make that first call outside any stream capture.
+ *   Sharing: all calls on a device use the same array and it keeps the previous
+ *   call's contents (nothing needs clearing: every slot read is written earlier
+ *   in the same call).  Calls that overlap on the GPU race on it; keep them on
+ *   one stream or order them with events. */
+#define BIDMAT_B200_NOALLOC_SCRATCH_FLOATS (4 * 1024 * 1024)
+#define BIDMAT_B200_NOALLOC_MAX_CHUNK 16384
+BIDMAT_B200_API int bidmat_b200_dsmult_noalloc(int nrows, int ncols, int nnz, const float *A,
+                                               const float *Bdata, const int *Bir, const int *Bic,
+                                               float *C, bidmat_stream_t stream);
+
 /* Structure helpers on the device (the steps BIDMat performs around the path
  * with cuSPARSE csr2coo and a host loop: GSMat.fromSMat, GSMat.scala:639, and
  * SparseMat.compressInds, SparseMat.scala:857-868).
