@@ -23,18 +23,23 @@ def _ck(err, what):
         raise RuntimeError("%s: %s" % (what, _lib.error_string(err)))
 
 
+def slice_columns(jc, ir, data, col0, col1):
+    """Columns [col0, col1) of a CSC matrix with re-based, zero-based column
+    pointers (what GSMat.colslice produces).  Pure tensor slicing: works on CPU
+    and CUDA tensors alike."""
+    j0, j1 = int(jc[col0]), int(jc[col1])
+    return (jc[col0:col1 + 1] - j0).to(torch.int32).contiguous(), ir[j0:j1].contiguous(), data[j0:j1].contiguous()
+
+
 class ColumnShard:
     """Device tensors of one column range of a CSC matrix."""
 
     def __init__(self, m, jc, ir, data, col0, col1):
-        j0, j1 = int(jc[col0]), int(jc[col1])
         self.m = int(m)
         self.col0, self.col1 = int(col0), int(col1)
         self.n = self.col1 - self.col0
-        self.nnz = j1 - j0
-        self.jc = (jc[col0:col1 + 1] - j0).to(torch.int32).contiguous()
-        self.ir = ir[j0:j1].contiguous()
-        self.data = data[j0:j1].contiguous()
+        self.jc, self.ir, self.data = slice_columns(jc, ir, data, col0, col1)
+        self.nnz = int(self.ir.numel())
         self.ic = torch.empty(self.nnz, dtype=torch.int32, device=ir.device)
         if self.nnz:
             _ck(_L.bidmat_b200_expand_jc(self.n, self.nnz, self.jc.data_ptr(), self.ic.data_ptr(),
