@@ -113,23 +113,47 @@ struct WorkspaceLease {
 inline size_t pad256(size_t b) { return (b + 255) & ~size_t(255); }
 
 // O[:, seg[j]] += val[j] * D[:, gidx[j]] with `part` holding 2*nchunks*k floats.
+constexpr int kFastThreads = 128;
+
+// k = 4*lpv*nt exactly and 16-byte aligned operands: the predicate-free kernels apply.
+bool fast_shape(int k, const Shape &s) { return s.vec == 4 && s.tiles == 1 && k == 4 * s.lpv * s.nt; }
+
 cudaError_t launch_ga(int k, long long nnz, const float *D, const float *val, const int *gidx,
                       const int *seg, float *O, float *part, int chunk, const Shape &s,
                       cudaStream_t st, const char *label) {
     const long long nchunks = (nnz + chunk - 1) / chunk;
     dim3 grid(blocks_for(nchunks, s.lpv), s.tiles, 1);
+    if (fast_shape(k, s) && !env_int("BIDMAT_B200_GENERIC", 0)) {
+        const int wpb = kFastThreads / s.lpv;
+        dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
+        const int deep = env_int("BIDMAT_B200_GA_DEEP", 0);
+        ScopedSpan sp(label, st);
+#define CALL_FAST(LPV, NT, U)                                                                          \
+    ga_chunk_fast_kernel<LPV, NT, U, kFastThreads><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, D, val, \
+                                                                                  gidx, seg, O, part)
+        if (s.lpv == 8) CALL_FAST(8, 1, 4);
+        else if (s.lpv == 16) CALL_FAST(16, 1, 4);
+        else if (s.nt == 1) { if (deep) CALL_FAST(32, 1, 8); else CALL_FAST(32, 1, 4); }
+        else if (s.nt == 2) { if (deep) CALL_FAST(32, 2, 4); else CALL_FAST(32, 2, 2); }
+        else { if (deep) CALL_FAST(32, 4, 2); else CALL_FAST(32, 4, 1); }
+#undef CALL_FAST
+    } else {
 #define CALL_GA(VEC, LPV, NT)                                                                   \
     {                                                                                           \
         ScopedSpan sp(label, st);                                                               \
         ga_chunk_kernel<VEC, LPV, NT, 4><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, D, val, \
                                                                     gidx, seg, O, part);        \
-    }                                                                                           \
-    if (nchunks > 1) {                                                                          \
-        ScopedSpan sp("ga_fixup", st);                                                          \
-        ga_fixup_kernel<VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, seg, O, part); \
     }
-    DISPATCH_SHAPE(s, CALL_GA);
+        DISPATCH_SHAPE(s, CALL_GA);
 #undef CALL_GA
+    }
+    if (nchunks > 1) {
+        ScopedSpan sp("ga_fixup", st);
+#define CALL_FIX(VEC, LPV, NT) \
+    ga_fixup_kernel<VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, seg, O, part);
+        DISPATCH_SHAPE(s, CALL_FIX);
+#undef CALL_FIX
+    }
     g_launches += (nchunks > 1) ? 2 : 1;
     return cudaGetLastError();
 }
@@ -142,11 +166,20 @@ cudaError_t launch_dds(int k, long long nnz, const float *A, const float *B, con
     const long long nchunks = (nnz + chunk - 1) / chunk;
     dim3 grid(blocks_for(nchunks, s.lpv), 1, 1);
     ScopedSpan sp("dds_chunk", st);
+    if (fast_shape(k, s) && s.lpv == 32 && s.nt <= 2 && !env_int("BIDMAT_B200_GENERIC", 0)) {
+        const int wpb = kFastThreads / 32;
+        dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
+        if (s.nt == 1)
+            dds_chunk_fast_kernel<1, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
+        else
+            dds_chunk_fast_kernel<2, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
+    } else {
 #define CALL_DDS(VEC, LPV, NT)                                                                  \
     dds_chunk_kernel<VEC, LPV, NT, 4, ACCUM><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, A, B, \
                                                                         ir, ic, P);
-    DISPATCH_SHAPE(s, CALL_DDS);
+        DISPATCH_SHAPE(s, CALL_DDS);
 #undef CALL_DDS
+    }
     g_launches += 1;
     return cudaGetLastError();
 }

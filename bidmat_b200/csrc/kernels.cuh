@@ -164,6 +164,278 @@ ga_fixup_kernel(int k, long long nnz, int chunk, long long nchunks,
 }
 
 // ---------------------------------------------------------------------------
+// Fast paths for the common dense heights k = 4*LPV*NT (32, 64, 128, 256, 512)
+// with 16-byte aligned operands: every lane owns exactly NT float4 of a
+// column, so no bounds predicates are needed.
+//
+// The (index, value, segment) triples of the next LPV nonzeros are staged in
+// shared memory with cp.async while the current LPV are processed, so the
+// gathers never wait for an index load and the triple of nonzero t is one
+// broadcast 16-byte shared load instead of three shuffles.  Gathers are issued
+// U columns ahead of the FMAs that consume them (two register buffers), so a
+// worker always has U..2U column loads in flight.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async4(void *smem_dst, const void *gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+template <int LPV> __device__ __forceinline__ void worker_sync(unsigned mask) {
+    __syncwarp(mask);
+}
+
+template <int LPV, int NT, int U, int TPB>
+__global__ void __launch_bounds__(TPB)
+ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
+                     const float *__restrict__ D, const float *__restrict__ val,
+                     const int *__restrict__ gidx, const int *__restrict__ seg,
+                     float *__restrict__ O, float *__restrict__ part) {
+    constexpr int K = 4 * LPV * NT;        // dense height handled by this instantiation
+    constexpr int WPB = TPB / LPV;         // workers per CTA
+    constexpr int G = LPV / U;             // groups of U nonzeros per staged batch
+    static_assert(LPV % U == 0, "U must divide LPV");
+    __shared__ int4 meta[WPB][2][LPV];     // {gather index, value bits, segment, unused}
+
+    const int lane = threadIdx.x & (LPV - 1);
+    const int w = threadIdx.x / LPV;
+    const unsigned mask = worker_mask<LPV>();
+    const long long c = (long long)blockIdx.x * WPB + w;
+    if (c >= nchunks) return;
+
+    const long long j0 = c * (long long)chunk;
+    const long long j1 = (j0 + chunk < nnz) ? j0 + chunk : nnz;
+    const int nb = (int)((j1 - j0 + LPV - 1) / LPV);
+    const float *Dl = D + lane * 4;        // this lane's first float4 inside any column
+
+    auto stage = [&](int buf, long long base) {
+        const long long jj = base + lane;
+        int4 *dst = &meta[w][buf][lane];
+        if (jj < j1) {
+            cp_async4(&dst->x, gidx + jj);
+            cp_async4(&dst->y, val + jj);
+            cp_async4(&dst->z, seg + jj);
+        } else {
+            // padding of the last batch: repeat the last nonzero with value 0
+            *dst = make_int4(__ldg(gidx + j1 - 1), 0, __ldg(seg + j1 - 1), 0);
+        }
+        cp_async_commit();
+    };
+
+    int cur = __ldg(seg + j0);
+    bool head_open = (j0 > 0) && (__ldg(seg + j0 - 1) == cur);
+    float4 acc[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    auto flush = [&](bool tail_open) {
+        if (!head_open && !tail_open) {
+            float4 *o = reinterpret_cast<float4 *>(O + (size_t)cur * K) + lane;
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+                float4 old = o[t * LPV];
+                old.x += acc[t].x; old.y += acc[t].y; old.z += acc[t].z; old.w += acc[t].w;
+                o[t * LPV] = old;
+            }
+        } else {
+            float4 *p = reinterpret_cast<float4 *>(part + ((size_t)c * 2 + (head_open ? 0 : 1)) * K) + lane;
+#pragma unroll
+            for (int t = 0; t < NT; t++) p[t * LPV] = acc[t];
+        }
+    };
+
+    stage(0, j0);
+    for (int b = 0; b < nb; b++) {
+        if (b + 1 < nb) {
+            stage((b + 1) & 1, j0 + (long long)(b + 1) * LPV);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        worker_sync<LPV>(mask);
+        const int4 *mt = meta[w][b & 1];
+
+        float4 x[2][U][NT];
+        int4 e[2][U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            e[0][u] = mt[u];
+            const float4 *d = reinterpret_cast<const float4 *>(Dl + (size_t)e[0][u].x * K);
+#pragma unroll
+            for (int t = 0; t < NT; t++) x[0][u][t] = __ldg(d + t * LPV);
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            if (g + 1 < G) {
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    e[(g + 1) & 1][u] = mt[(g + 1) * U + u];
+                    const float4 *d = reinterpret_cast<const float4 *>(Dl + (size_t)e[(g + 1) & 1][u].x * K);
+#pragma unroll
+                    for (int t = 0; t < NT; t++) x[(g + 1) & 1][u][t] = __ldg(d + t * LPV);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int4 m = e[g & 1][u];
+                if (m.z != cur) {
+                    flush(false);
+                    cur = m.z;
+                    head_open = false;
+#pragma unroll
+                    for (int t = 0; t < NT; t++) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                const float v = __int_as_float(m.y);
+#pragma unroll
+                for (int t = 0; t < NT; t++) {
+                    const float4 xv = x[g & 1][u][t];
+                    acc[t].x = fmaf(v, xv.x, acc[t].x); acc[t].y = fmaf(v, xv.y, acc[t].y);
+                    acc[t].z = fmaf(v, xv.z, acc[t].z); acc[t].w = fmaf(v, xv.w, acc[t].w);
+                }
+            }
+        }
+        worker_sync<LPV>(mask);   // everyone is done with this buffer before it is staged again
+    }
+    const bool tail_open = (j1 < nnz) && (__ldg(seg + j1) == cur);
+    flush(tail_open);
+}
+
+// Sampled dense-dense product, fast path (k = 4*32*NT, full warps).  The dot
+// products of 8 consecutive nonzeros are reduced together: three exchange
+// steps halve the number of live partials while doubling the lanes summed,
+// then two plain xor steps finish, 9 shuffles per 8 nonzeros instead of 40.
+// After four such groups lane l holds the result of nonzero (l&3)*8 + (l>>2)
+// of the batch, and the 32 results go out as one 128-byte store.
+template <int NT, int TPB, bool ACCUM>
+__global__ void __launch_bounds__(TPB)
+dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
+                      const float *__restrict__ A, const float *__restrict__ B,
+                      const int *__restrict__ ir, const int *__restrict__ ic, float *__restrict__ P) {
+    constexpr int LPV = 32;
+    constexpr int K = 4 * LPV * NT;
+    constexpr int WPB = TPB / LPV;
+    constexpr int U = 4;
+    __shared__ int2 meta[WPB][2][LPV];     // {row, column}
+
+    const int lane = threadIdx.x & 31;
+    const int w = threadIdx.x >> 5;
+    const unsigned mask = 0xffffffffu;
+    const long long c = (long long)blockIdx.x * WPB + w;
+    if (c >= nchunks) return;
+    const long long j0 = c * (long long)chunk;
+    const long long j1 = (j0 + chunk < nnz) ? j0 + chunk : nnz;
+    const int nb = (int)((j1 - j0 + LPV - 1) / LPV);
+    const float *Al = A + lane * 4;
+    const float *Bl = B + lane * 4;
+
+    auto stage = [&](int buf, long long base) {
+        const long long jj = base + lane;
+        int2 *dst = &meta[w][buf][lane];
+        if (jj < j1) {
+            cp_async4(&dst->x, ir + jj);
+            cp_async4(&dst->y, ic + jj);
+        } else {
+            *dst = make_int2(__ldg(ir + j1 - 1), __ldg(ic + j1 - 1));
+        }
+        cp_async_commit();
+    };
+
+    int cur = -1;
+    float4 bv[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) bv[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    stage(0, j0);
+    for (int b = 0; b < nb; b++) {
+        const long long base = j0 + (long long)b * LPV;
+        if (b + 1 < nb) {
+            stage((b + 1) & 1, base + LPV);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp(mask);
+        const int2 *mt = meta[w][b & 1];
+        // my own result slot of this batch; start its read-modify-write early
+        const int myslot = (lane & 3) * 8 + (lane >> 2);
+        const long long myj = base + myslot;
+        float old = 0.f;
+        if (ACCUM && myj < j1) old = P[myj];
+        float mine = 0.f;
+
+        float4 x[2][U][NT];
+        int2 e[2][U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            e[0][u] = mt[u];
+            const float4 *a = reinterpret_cast<const float4 *>(Al + (size_t)e[0][u].x * K);
+#pragma unroll
+            for (int t = 0; t < NT; t++) x[0][u][t] = __ldg(a + t * LPV);
+        }
+        float p[8];
+#pragma unroll
+        for (int g = 0; g < LPV / U; g++) {
+            if (g + 1 < LPV / U) {
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    e[(g + 1) & 1][u] = mt[(g + 1) * U + u];
+                    const float4 *a = reinterpret_cast<const float4 *>(Al + (size_t)e[(g + 1) & 1][u].x * K);
+#pragma unroll
+                    for (int t = 0; t < NT; t++) x[(g + 1) & 1][u][t] = __ldg(a + t * LPV);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int col = e[g & 1][u].y;
+                if (col != cur) {
+                    cur = col;
+                    const float4 *bp = reinterpret_cast<const float4 *>(Bl + (size_t)cur * K);
+#pragma unroll
+                    for (int t = 0; t < NT; t++) bv[t] = __ldg(bp + t * LPV);
+                }
+                float s = 0.f;
+#pragma unroll
+                for (int t = 0; t < NT; t++) {
+                    const float4 xv = x[g & 1][u][t];
+                    s = fmaf(xv.x, bv[t].x, s); s = fmaf(xv.y, bv[t].y, s);
+                    s = fmaf(xv.z, bv[t].z, s); s = fmaf(xv.w, bv[t].w, s);
+                }
+                p[(g & 1) * U + u] = s;
+            }
+            if (g & 1) {
+                // reduce the 8 partial dot products p[0..7] of nonzeros 8*(g/2) .. 8*(g/2)+7
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float give = (lane & 16) ? p[i] : p[i + 4];
+                    const float keep = (lane & 16) ? p[i + 4] : p[i];
+                    p[i] = keep + __shfl_xor_sync(mask, give, 16);
+                }
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const float give = (lane & 8) ? p[i] : p[i + 2];
+                    const float keep = (lane & 8) ? p[i + 2] : p[i];
+                    p[i] = keep + __shfl_xor_sync(mask, give, 8);
+                }
+                {
+                    const float give = (lane & 4) ? p[0] : p[1];
+                    const float keep = (lane & 4) ? p[1] : p[0];
+                    p[0] = keep + __shfl_xor_sync(mask, give, 4);
+                }
+                p[0] += __shfl_xor_sync(mask, p[0], 2);
+                p[0] += __shfl_xor_sync(mask, p[0], 1);
+                // lane l now holds the dot product of nonzero (l >> 2) of this group of 8
+                if ((lane & 3) == (g >> 1)) mine = p[0];
+            }
+        }
+        if (myj < j1) P[myj] = ACCUM ? old + mine : mine;
+        __syncwarp(mask);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Sampled dense-dense product:  P[j] (+)= <A[:, ir[j]], B[:, ic[j]]>
 //
 // One worker per chunk of nonzeros.  The B column is kept in registers while
