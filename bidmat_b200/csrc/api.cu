@@ -3,8 +3,6 @@
 // the row-sort that turns the CSC nonzero list into the row-major order B*^S
 // needs.  Built for sm_100a only.
 #include <cuda_runtime.h>
-#include <cub/device/device_radix_sort.cuh>
-#include <cub/device/device_reduce.cuh>
 
 #include <atomic>
 #include <cstdint>
@@ -16,6 +14,7 @@
 #include "../../include/bidmat_b200.h"
 #include "kernels.cuh"
 #include "structure_kernels.cuh"
+#include "rowsort.cuh"
 #include "host_common.cuh"
 
 using namespace bidmat;
@@ -118,10 +117,16 @@ constexpr int kFastThreads = 128;
 // k = 4*lpv*nt exactly and 16-byte aligned operands: the predicate-free kernels apply.
 bool fast_shape(int k, const Shape &s) { return s.vec == 4 && s.tiles == 1 && k == 4 * s.lpv * s.nt; }
 
+// `count` nonzeros are processed: the whole list (range == nullptr, count == nnz) or
+// the slice [range[0], range[1]) read on the device.  The output column of a
+// nonzero is seg & segmask.
 cudaError_t launch_ga(int k, long long nnz, const float *D, const float *val, const int *gidx,
                       const int *seg, float *O, float *part, int chunk, const Shape &s,
-                      cudaStream_t st, const char *label) {
-    const long long nchunks = (nnz + chunk - 1) / chunk;
+                      cudaStream_t st, const char *label, long long count = -1,
+                      const int *range = nullptr, unsigned segmask = 0xffffffffu) {
+    if (count < 0) count = nnz;
+    if (count == 0) return cudaSuccess;
+    const long long nchunks = (count + chunk - 1) / chunk;
     dim3 grid(blocks_for(nchunks, s.lpv), s.tiles, 1);
     if (fast_shape(k, s) && !env_int("BIDMAT_B200_GENERIC", 0)) {
         const int wpb = kFastThreads / s.lpv;
@@ -130,7 +135,7 @@ cudaError_t launch_ga(int k, long long nnz, const float *D, const float *val, co
         ScopedSpan sp(label, st);
 #define CALL_FAST(LPV, NT, U)                                                                          \
     ga_chunk_fast_kernel<LPV, NT, U, kFastThreads><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, D, val, \
-                                                                                  gidx, seg, O, part)
+                                                                                  gidx, seg, O, part, range, segmask)
         if (s.lpv == 8) CALL_FAST(8, 1, 4);
         else if (s.lpv == 16) CALL_FAST(16, 1, 4);
         else if (s.nt == 1) { if (deep) CALL_FAST(32, 1, 8); else CALL_FAST(32, 1, 4); }
@@ -142,7 +147,8 @@ cudaError_t launch_ga(int k, long long nnz, const float *D, const float *val, co
     {                                                                                           \
         ScopedSpan sp(label, st);                                                               \
         ga_chunk_kernel<VEC, LPV, NT, 4><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, D, val, \
-                                                                    gidx, seg, O, part);        \
+                                                                    gidx, seg, O, part, range,  \
+                                                                    segmask);                   \
     }
         DISPATCH_SHAPE(s, CALL_GA);
 #undef CALL_GA
@@ -150,7 +156,7 @@ cudaError_t launch_ga(int k, long long nnz, const float *D, const float *val, co
     if (nchunks > 1) {
         ScopedSpan sp("ga_fixup", st);
 #define CALL_FIX(VEC, LPV, NT) \
-    ga_fixup_kernel<VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, seg, O, part);
+    ga_fixup_kernel<VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, seg, O, part, range, segmask);
         DISPATCH_SHAPE(s, CALL_FIX);
 #undef CALL_FIX
     }
@@ -228,61 +234,141 @@ int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, con
     cudaStream_t st = as_stream(stream);
     const size_t n = (size_t)nnz;
     const Shape s = pick_shape(nrows, is16(A) && is16(C));
-    const int chunk = pick_chunk(nnz, s.lpv);
 
-    size_t sort_tmp = 0, red_tmp = 0;
-    cudaError_t err = cub::DeviceRadixSort::SortPairs(nullptr, sort_tmp, (const int *)nullptr, (int *)nullptr,
-                                                      (const int *)nullptr, (int *)nullptr, n, 0, 32, st);
-    if (err != cudaSuccess) return (int)err;
-    err = cub::DeviceReduce::Max(nullptr, red_tmp, (const int *)nullptr, (int *)nullptr, n, st);
-    if (err != cudaSuccess) return (int)err;
-    const size_t tmp_bytes = sort_tmp > red_tmp ? sort_tmp : red_tmp;
-    const size_t part_floats = ga_part_floats(nrows, nnz, chunk);
-    size_t need = pad256(tmp_bytes) + 5 * pad256(n * 4) + pad256(part_floats * 4) + 1024;
+    // Column blocks: when the dense operand is much larger than L2, the nonzeros
+    // are ordered by (column block, row) so that the gathers of one block stay
+    // L2-resident; blocks are then processed one after the other.
+    const size_t dense_bytes = (size_t)ncols * (size_t)nrows * sizeof(float);
+    const size_t block_bytes = (size_t)env_int("BIDMAT_B200_COLBLOCK_MB", 64) << 20;
+    int colshift = 31;
+    const int forced_cols = env_int("BIDMAT_B200_COLBLOCK_COLS", 0);   // tests force tiny blocks
+    if (forced_cols > 0) {
+        colshift = 0;
+        while ((2 << colshift) <= forced_cols) colshift++;
+    } else if (block_bytes > 0 && dense_bytes > block_bytes + block_bytes / 2) {
+        size_t cols_per_block = block_bytes / ((size_t)nrows * sizeof(float));
+        colshift = 0;
+        while ((2ull << colshift) <= cols_per_block) colshift++;
+    }
+
+    const int ntiles = (int)((n + kSortTile - 1) / kSortTile);
+    size_t need = 6 * pad256(n * 4) + pad256((size_t)256 * ntiles * 4) + 4 * pad256(4096) + pad256(256 * kSortScanSegs * 4) + 4096;
+    // Partial-sum scratch: enough chunk slots for the whole list or for any single
+    // column block, whichever chunk length pick_chunk gives them.
+    const int chunk_all = pick_chunk(nnz, s.lpv);
+    const long long cap_chunks = max_chunks_for(nnz, s.lpv);
+    const size_t part_floats = (size_t)cap_chunks * 2 * (size_t)nrows;
+    need += pad256(part_floats * 4);
     WorkspaceLease ws(need, st);
     if (ws.err != cudaSuccess) return (int)ws.err;
-    char *tmp = ws.take<char>(tmp_bytes);
-    int *iota = ws.take<int>(n);
-    int *rows_sorted = ws.take<int>(n);
-    int *perm = ws.take<int>(n);
-    int *cols_sorted = ws.take<int>(n);
-    float *vals_sorted = ws.take<float>(n);
-    float *part = ws.take<float>(part_floats);
+    unsigned *keys[2] = {ws.take<unsigned>(n), ws.take<unsigned>(n)};
+    int *cols[2] = {ws.take<int>(n), ws.take<int>(n)};
+    float *vals[2] = {ws.take<float>(n), ws.take<float>(n)};
+    int *counts = ws.take<int>((size_t)256 * ntiles);
+    int *totals = ws.take<int>(256 * kSortScanSegs);   // per (digit, scan segment)
     int *maxrow = ws.take<int>(1);
+    int *offsets = ws.take<int>(1024);
+    float *part = ws.take<float>(part_floats);
 
-    int bits = 32;
+    cudaError_t err;
+    int rowbits;
     if (m_hint > 0) {
-        bits = ceil_log2((unsigned long long)m_hint);
+        rowbits = ceil_log2((unsigned long long)m_hint);
     } else {
-        size_t t = tmp_bytes;
-        err = cub::DeviceReduce::Max(tmp, t, Bir, maxrow, n, st);
+        err = cudaMemsetAsync(maxrow, 0, sizeof(int), st);
         if (err != cudaSuccess) return (int)err;
+        max_int_kernel<<<148 * 8, 256, 0, st>>>(nnz, Bir, maxrow);
+        g_launches += 1;
         int h = 0;
         err = cudaMemcpyAsync(&h, maxrow, sizeof(int), cudaMemcpyDeviceToHost, st);
-        if (err != cudaSuccess) return (int)err;
-        err = cudaStreamSynchronize(st);
+        if (err == cudaSuccess) err = cudaStreamSynchronize(st);
         if (err != cudaSuccess) return (int)err;
         if (h < 0) return (int)cudaErrorInvalidValue;
-        bits = ceil_log2((unsigned long long)h + 1);
+        rowbits = ceil_log2((unsigned long long)h + 1);
     }
-    if (bits < 1) bits = 1;
-    if (bits > 31) bits = 31;
+    if (rowbits < 1) rowbits = 1;
+    if (rowbits > 31) return (int)cudaErrorInvalidValue;
+    int nblocks = (colshift >= 31) ? 1 : (((ncols - 1) >> colshift) + 1);
+    while (nblocks > 1 && (rowbits + ceil_log2((unsigned long long)nblocks) > 32 || nblocks > 1023)) {
+        colshift++;
+        nblocks = ((ncols - 1) >> colshift) + 1;
+    }
+    if (nblocks <= 1) { colshift = 31; nblocks = 1; }
+    const int keybits = rowbits + (nblocks > 1 ? ceil_log2((unsigned long long)nblocks) : 0);
+    const int passes = (keybits + 7) / 8;
+    const SortKeySpec ks{colshift, rowbits};
+    const unsigned rowmask = (rowbits >= 32) ? 0xffffffffu : ((1u << rowbits) - 1u);
 
-    const unsigned nb = (unsigned)((n + kThreads - 1) / kThreads);
-    ScopedSpan *sort_span = new ScopedSpan("dsmultT_rowsort", st);
-    iota_kernel<<<nb, kThreads, 0, st>>>(nnz, iota);
-    g_launches += 1;
-    size_t t = tmp_bytes;
-    // Stable LSD radix sort by row: equal rows keep ascending nonzero order,
-    // i.e. ascending source column, the order the reference CPU loop adds in.
-    err = cub::DeviceRadixSort::SortPairs(tmp, t, Bir, rows_sorted, iota, perm, n, 0, bits, st);
-    if (err != cudaSuccess) { delete sort_span; return (int)err; }
-    permute_pairs_kernel<<<nb, kThreads, 0, st>>>(nnz, perm, Bic, Bdata, cols_sorted, vals_sorted);
-    g_launches += 1;
-    delete sort_span;
+    static std::once_flag smem_once[kMaxDevices];
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        std::call_once(smem_once[dev], [] {
+            cudaFuncSetAttribute(sort_scatter_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem));
+            cudaFuncSetAttribute(sort_scatter_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem));
+        });
+    }
+
+    int cur = 0;   // buffer holding the output of the last pass
+    {
+        ScopedSpan sp("dsmultT_rowsort", st);
+        const int tps = (ntiles + kSortScanSegs - 1) / kSortScanSegs;   // tiles per scan segment
+        for (int p = 0; p < passes; p++) {
+            const int shift = 8 * p;
+            const int out = (p == 0) ? 0 : 1 - cur;
+            {
+                ScopedSpan sp1("sort_hist", st);
+                if (p == 0) {
+                    sort_hist_kernel<true><<<ntiles, kSortThreads, 0, st>>>(nnz, ntiles, shift, ks, nullptr, Bir, Bic, counts);
+                } else {
+                    sort_hist_kernel<false><<<ntiles, kSortThreads, 0, st>>>(nnz, ntiles, shift, ks, keys[cur], nullptr, nullptr, counts);
+                }
+            }
+            {
+                ScopedSpan sp2("sort_scan", st);
+                sort_scan_kernel<<<dim3(kSortScanSegs, 256), kSortThreads, 0, st>>>(ntiles, tps, counts, totals);
+                sort_digit_base_kernel<<<1, 256, 0, st>>>(totals);
+            }
+            {
+                ScopedSpan sp3("sort_scatter", st);
+                if (p == 0) {
+                    sort_scatter_kernel<true><<<ntiles, kSortThreads, sizeof(SortSmem), st>>>(
+                        nnz, ntiles, shift, ks, nullptr, Bir, Bic, Bdata, counts, totals, tps, keys[out], cols[out], vals[out]);
+                } else {
+                    sort_scatter_kernel<false><<<ntiles, kSortThreads, sizeof(SortSmem), st>>>(
+                        nnz, ntiles, shift, ks, keys[cur], nullptr, cols[cur], vals[cur], counts, totals, tps, keys[out],
+                        cols[out], vals[out]);
+                }
+            }
+            g_launches += 4;
+            cur = out;
+        }
+    }
     err = cudaGetLastError();
     if (err != cudaSuccess) return (int)err;
-    return (int)launch_ga(nrows, nnz, A, vals_sorted, cols_sorted, rows_sorted, C, part, chunk, s, st, "dsmultT_ga_chunk");
+    const int *seg = reinterpret_cast<const int *>(keys[cur]);
+
+    if (nblocks == 1) {
+        return (int)launch_ga(nrows, nnz, A, vals[cur], cols[cur], seg, C, part, chunk_all, s, st, "dsmultT_ga_chunk",
+                              nnz, nullptr, rowmask);
+    }
+    // slice boundaries of the column blocks in the sorted list
+    block_offsets_kernel<<<(nblocks + 256) / 256, 256, 0, st>>>(nnz, nblocks, rowbits, keys[cur], offsets);
+    g_launches += 1;
+    std::vector<int> h_off((size_t)nblocks + 1);
+    err = cudaMemcpyAsync(h_off.data(), offsets, sizeof(int) * (nblocks + 1), cudaMemcpyDeviceToHost, st);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+    if (err != cudaSuccess) return (int)err;
+    for (int b = 0; b < nblocks; b++) {
+        const long long count = (long long)h_off[b + 1] - h_off[b];
+        if (count <= 0) continue;
+        int chunk = pick_chunk(count, s.lpv);
+        if (ga_part_floats(nrows, count, chunk) > part_floats) chunk = chunk_all;
+        err = launch_ga(nrows, nnz, A, vals[cur], cols[cur], seg, C, part, chunk, s, st, "dsmultT_ga_chunk", count,
+                        offsets + b, rowmask);
+        if (err != cudaSuccess) return (int)err;
+    }
+    return 0;
 }
 
 int bidmat_b200_dds_async(int nrows, int nnz, const float *A, const float *B, const int *Cir,

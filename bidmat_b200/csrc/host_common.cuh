@@ -43,21 +43,33 @@ inline int env_int(const char *name, int dflt) {
     return atoi(v);
 }
 
-// Chunk length: aim at about 64K chunks so that the hardware scheduler can
-// balance them over 148 SMs, but never fewer than 64 nor more than 4096
-// nonzeros per chunk.  BIDMAT_B200_CHUNK overrides (tests use tiny chunks to
-// force runs across chunk boundaries).
+// Chunk length: about kTargetChunks chunks per launch (8 per resident worker
+// slot of a 148-SM part), never fewer than 64 nor more than 4096 nonzeros per
+// chunk.  BIDMAT_B200_CHUNK overrides (tests use tiny chunks to force runs
+// across chunk boundaries).
+constexpr long long kTargetChunks = 148LL * 16 * 8;
+
 inline int pick_chunk(long long nnz, int lpv) {
     int forced = env_int("BIDMAT_B200_CHUNK", 0);
     long long c;
     if (forced > 0) c = forced;
     else {
-        c = (nnz + 65535) / 65536;
+        c = (nnz + kTargetChunks - 1) / kTargetChunks;
         if (c < 64) c = 64;
         if (c > 4096) c = 4096;
     }
     c = ((c + lpv - 1) / lpv) * lpv;
     return (int)c;
+}
+
+// Upper bound on the number of chunks pick_chunk can give to the whole list of
+// nnz nonzeros or to any slice of it.
+inline long long max_chunks_for(long long nnz, int lpv) {
+    const int chunk_all = pick_chunk(nnz, lpv);
+    long long cap = (nnz + chunk_all - 1) / chunk_all;
+    long long by64 = (nnz + 63) / 64 + 1;
+    long long alt = by64 < kTargetChunks + 1 ? by64 : kTargetChunks + 1;
+    return alt > cap ? alt : cap;
 }
 
 #define DISPATCH_SHAPE(S, CALL)                                                     \

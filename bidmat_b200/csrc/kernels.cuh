@@ -29,7 +29,8 @@ __global__ void __launch_bounds__(kThreads)
 ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
                 const float *__restrict__ D, const float *__restrict__ val,
                 const int *__restrict__ gidx, const int *__restrict__ seg,
-                float *__restrict__ O, float *__restrict__ part) {
+                float *__restrict__ O, float *__restrict__ part,
+                const int *__restrict__ range, unsigned segmask) {
     typedef Vec<VEC> V;
     typedef typename V::T VT;
     const int lane = threadIdx.x & (LPV - 1);
@@ -46,10 +47,15 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
         eok[t] = eoff[t] < k;
     }
 
-    const long long j0 = c * (long long)chunk;
-    const long long j1 = (j0 + chunk < nnz) ? j0 + chunk : nnz;
+    // [lo, hi) is the slice of the nonzero list this launch works on (the whole
+    // list unless `range` points at two offsets); chunks are counted from lo.
+    const long long lo = range ? (long long)__ldg(range) : 0;
+    const long long hi = range ? (long long)__ldg(range + 1) : nnz;
+    const long long j0 = lo + c * (long long)chunk;
+    if (j0 >= hi) return;
+    const long long j1 = (j0 + chunk < hi) ? j0 + chunk : hi;
     int cur = __ldg(seg + j0);
-    bool head_open = (j0 > 0) && (__ldg(seg + j0 - 1) == cur);
+    bool head_open = (j0 > lo) && (__ldg(seg + j0 - 1) == cur);
 
     VT acc[NT];
 #pragma unroll
@@ -57,7 +63,7 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
 
     auto flush = [&](bool tail_open) {
         if (!head_open && !tail_open) {
-            float *o = O + (size_t)cur * k;
+            float *o = O + (size_t)((unsigned)cur & segmask) * k;
 #pragma unroll
             for (int t = 0; t < NT; t++)
                 if (eok[t]) {
@@ -110,29 +116,41 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
             }
         }
     }
-    const bool tail_open = (j1 < nnz) && (__ldg(seg + j1) == cur);
+    const bool tail_open = (j1 < hi) && (__ldg(seg + j1) == cur);
     flush(tail_open);
 }
 
 // One worker per chunk.  The worker whose chunk holds the START of a run that
-// leaves the chunk to the right walks the following chunks, adds the stored
-// pieces in chunk order and adds the total to O.  Every other worker returns.
+// leaves the chunk to the right finds the chunk in which the run ends (binary
+// search: seg is non-decreasing as unsigned keys), adds the stored pieces in
+// chunk order, with the loads issued four chunks ahead of the adds, and adds the
+// total to O.  Every other worker returns.
 template <int VEC, int LPV, int NT>
 __global__ void __launch_bounds__(kThreads)
 ga_fixup_kernel(int k, long long nnz, int chunk, long long nchunks,
                 const int *__restrict__ seg, float *__restrict__ O,
-                const float *__restrict__ part) {
+                const float *__restrict__ part, const int *__restrict__ range, unsigned segmask) {
     typedef Vec<VEC> V;
     typedef typename V::T VT;
     const int lane = threadIdx.x & (LPV - 1);
     const long long c = ((long long)blockIdx.x * kThreads + threadIdx.x) / LPV;
     if (c >= nchunks) return;
-    const long long j0 = c * (long long)chunk;
+    const long long lo = range ? (long long)__ldg(range) : 0;
+    const long long hi = range ? (long long)__ldg(range + 1) : nnz;
+    const long long j0 = lo + c * (long long)chunk;
     const long long j1 = j0 + chunk;
-    if (j1 >= nnz) return;
+    if (j1 >= hi) return;
     const int s = __ldg(seg + j1 - 1);
     if (__ldg(seg + j1) != s) return;                       // nothing leaves to the right
-    if (j0 > 0 && __ldg(seg + j0 - 1) == s) return;         // the run started further left
+    if (j0 > lo && __ldg(seg + j0 - 1) == s) return;        // the run started further left
+
+    // last position of the run: largest e in [j1, hi) with seg[e] == s
+    long long a = j1, b = hi;                               // invariant: seg[a] == s, seg[b] > s or b == hi
+    while (b - a > 1) {
+        const long long mid = (a + b) >> 1;
+        if ((unsigned)__ldg(seg + mid) <= (unsigned)s) a = mid; else b = mid;
+    }
+    const long long dend = (a - lo) / chunk;                // chunk holding the end of the run
 
     const int ktile = blockIdx.y * (LPV * NT * VEC);
     int eoff[NT];
@@ -144,16 +162,24 @@ ga_fixup_kernel(int k, long long nnz, int chunk, long long nchunks,
         eok[t] = eoff[t] < k;
         tot[t] = eok[t] ? V::ld(part + ((size_t)c * 2 + 1) * k + eoff[t]) : V::zero();
     }
-    for (long long d = c + 1; d < nchunks; d++) {
-        const float *p = part + (size_t)d * 2 * k;
+    constexpr int PF = 4;
+    for (long long d = c + 1; d <= dend; d += PF) {
+        VT x[PF][NT];
 #pragma unroll
-        for (int t = 0; t < NT; t++)
-            if (eok[t]) V::add(tot[t], V::ld(p + eoff[t]));
-        const long long dj1 = (d + 1) * (long long)chunk;
-        if (dj1 >= nnz) break;
-        if (__ldg(seg + dj1 - 1) != s || __ldg(seg + dj1) != s) break;  // run ends in chunk d
+        for (int q = 0; q < PF; q++) {
+            const long long dd = (d + q <= dend) ? d + q : dend;
+            const float *p = part + (size_t)dd * 2 * k;
+#pragma unroll
+            for (int t = 0; t < NT; t++) x[q][t] = eok[t] ? V::ld(p + eoff[t]) : V::zero();
+        }
+#pragma unroll
+        for (int q = 0; q < PF; q++)
+            if (d + q <= dend) {
+#pragma unroll
+                for (int t = 0; t < NT; t++) V::add(tot[t], x[q][t]);
+            }
     }
-    float *o = O + (size_t)s * k;
+    float *o = O + (size_t)((unsigned)s & segmask) * k;
 #pragma unroll
     for (int t = 0; t < NT; t++)
         if (eok[t]) {
@@ -193,7 +219,8 @@ __global__ void __launch_bounds__(TPB)
 ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
                      const float *__restrict__ D, const float *__restrict__ val,
                      const int *__restrict__ gidx, const int *__restrict__ seg,
-                     float *__restrict__ O, float *__restrict__ part) {
+                     float *__restrict__ O, float *__restrict__ part,
+                     const int *__restrict__ range, unsigned segmask) {
     constexpr int K = 4 * LPV * NT;        // dense height handled by this instantiation
     constexpr int WPB = TPB / LPV;         // workers per CTA
     constexpr int G = LPV / U;             // groups of U nonzeros per staged batch
@@ -206,8 +233,11 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     const long long c = (long long)blockIdx.x * WPB + w;
     if (c >= nchunks) return;
 
-    const long long j0 = c * (long long)chunk;
-    const long long j1 = (j0 + chunk < nnz) ? j0 + chunk : nnz;
+    const long long lo = range ? (long long)__ldg(range) : 0;
+    const long long hi = range ? (long long)__ldg(range + 1) : nnz;
+    const long long j0 = lo + c * (long long)chunk;
+    if (j0 >= hi) return;
+    const long long j1 = (j0 + chunk < hi) ? j0 + chunk : hi;
     const int nb = (int)((j1 - j0 + LPV - 1) / LPV);
     const float *Dl = D + lane * 4;        // this lane's first float4 inside any column
 
@@ -226,17 +256,29 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     };
 
     int cur = __ldg(seg + j0);
-    bool head_open = (j0 > 0) && (__ldg(seg + j0 - 1) == cur);
+    bool head_open = (j0 > lo) && (__ldg(seg + j0 - 1) == cur);
     float4 acc[NT];
+    float4 oldv[NT];   // current contents of the output column of the run, fetched when the run starts
 #pragma unroll
     for (int t = 0; t < NT; t++) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
 
+    // The read half of the output's read-modify-write is issued at the start of a
+    // run and only consumed when the run is flushed, so its latency overlaps the
+    // gathers of the run.  Only this worker touches that column during the launch
+    // (runs shared with a neighbour go to `part` instead), so the value cannot
+    // change in between.
+    auto prefetch_out = [&]() {
+        const float4 *o = reinterpret_cast<const float4 *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
+#pragma unroll
+        for (int t = 0; t < NT; t++) oldv[t] = o[t * LPV];
+    };
+
     auto flush = [&](bool tail_open) {
         if (!head_open && !tail_open) {
-            float4 *o = reinterpret_cast<float4 *>(O + (size_t)cur * K) + lane;
+            float4 *o = reinterpret_cast<float4 *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
 #pragma unroll
             for (int t = 0; t < NT; t++) {
-                float4 old = o[t * LPV];
+                float4 old = oldv[t];
                 old.x += acc[t].x; old.y += acc[t].y; old.z += acc[t].z; old.w += acc[t].w;
                 o[t * LPV] = old;
             }
@@ -248,6 +290,7 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     };
 
     stage(0, j0);
+    prefetch_out();
     for (int b = 0; b < nb; b++) {
         if (b + 1 < nb) {
             stage((b + 1) & 1, j0 + (long long)(b + 1) * LPV);
@@ -285,6 +328,7 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
                     flush(false);
                     cur = m.z;
                     head_open = false;
+                    prefetch_out();
 #pragma unroll
                     for (int t = 0; t < NT; t++) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
@@ -299,7 +343,7 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
         }
         worker_sync<LPV>(mask);   // everyone is done with this buffer before it is staged again
     }
-    const bool tail_open = (j1 < nnz) && (__ldg(seg + j1) == cur);
+    const bool tail_open = (j1 < hi) && (__ldg(seg + j1) == cur);
     flush(tail_open);
 }
 

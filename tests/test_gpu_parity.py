@@ -110,6 +110,57 @@ def test_runs_crossing_chunk_boundaries(cuda_device, k, chunk, monkeypatch):
     check_all_ops(k, m, n, jc, ir, data, cuda_device, rng)
 
 
+@pytest.mark.parametrize("cols_per_block", [1, 4, 16])
+@pytest.mark.parametrize("k", [12, 128, 256])
+def test_transposed_product_with_column_blocks(cuda_device, k, cols_per_block, monkeypatch):
+    """B*^S orders the nonzeros by (column block, row) when B is much larger
+    than L2 and runs the blocks one after the other; tiny forced blocks and
+    chunks exercise the slicing, the masking of the row bits and the fix-up
+    across block-local chunks."""
+    monkeypatch.setenv("BIDMAT_B200_COLBLOCK_COLS", str(cols_per_block))
+    monkeypatch.setenv("BIDMAT_B200_CHUNK", "32")
+    rng = np.random.default_rng(1000 * k + cols_per_block)
+    m, n = 300, 70
+    jc, ir, data = random_csc(m, n, 0.3, rng, empty_cols=(0, 1, 2, 3, 40, 69))
+    S = DeviceCSC(m, n, jc, ir, data, cuda_device)
+    B = rng.standard_normal((n, k)).astype(np.float32)
+    G0 = rng.standard_normal((m, k)).astype(np.float32)
+    G = abi_dsmultT(dev(B, cuda_device), S, dev(G0, cuda_device)).cpu().numpy()
+    Gw = oracle.dsmultT(B, data, ir, jc, m, out=G0.copy())
+    _, Gabs = oracle.dsmultT_f64(B, data, ir, jc, m)
+    assert_close_scaled(G, Gw, Gabs + np.abs(G0), RTOL_DSMULTT, "blocked B*^S")
+    G2 = abi_dsmultT(dev(B, cuda_device), S, dev(G0, cuda_device)).cpu().numpy()
+    assert np.array_equal(G.view(np.uint32), G2.view(np.uint32))
+
+
+def test_transposed_product_with_many_rows_needs_more_sort_passes(cuda_device):
+    """Row indices up to 2^21 and beyond: three and four 8-bit sort passes."""
+    rng = np.random.default_rng(77)
+    k = 8
+    for m in (70_000, 2_200_000, 17_000_000):
+        n = 50
+        nnz_per_col = 40
+        jc = np.arange(0, (n + 1) * nnz_per_col, nnz_per_col, dtype=np.int32)
+        ir = np.concatenate([np.sort(rng.choice(m, nnz_per_col, replace=False)) for _ in range(n)]).astype(np.int32)
+        ir[-1] = m - 1
+        ir[-nnz_per_col:] = np.sort(ir[-nnz_per_col:])
+        data = rng.uniform(0.1, 1, len(ir)).astype(np.float32)
+        S = DeviceCSC(m, n, jc, ir, data, cuda_device)
+        B = rng.standard_normal((n, k)).astype(np.float32)
+        G = abi_dsmultT(dev(B, cuda_device), S, torch.zeros((m, k), device=cuda_device))
+        rows = np.unique(ir)
+        Gs = G[torch.from_numpy(rows).long().to(cuda_device)].cpu().numpy()
+        want = np.zeros((m if m < 100_000 else 0, k), np.float32)
+        # compare only the touched rows against an fp64 scatter-add
+        acc = np.zeros((len(rows), k))
+        pos = np.searchsorted(rows, ir)
+        ic = S.ic_h
+        np.add.at(acc, pos, data[:, None].astype(np.float64) * B[ic].astype(np.float64))
+        assert np.abs(Gs - acc).max() <= 1e-4 * np.abs(acc).max()
+        assert float(G.abs().sum()) == pytest.approx(float(np.abs(Gs).sum()), rel=1e-5)   # nothing else was written
+        del G, want
+
+
 def test_single_huge_column_and_single_hot_row(cuda_device, monkeypatch):
     monkeypatch.setenv("BIDMAT_B200_CHUNK", "64")
     rng = np.random.default_rng(3)
