@@ -239,16 +239,29 @@ int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, con
     // are ordered by (column block, row) so that the gathers of one block stay
     // L2-resident; blocks are then processed one after the other.
     const size_t dense_bytes = (size_t)ncols * (size_t)nrows * sizeof(float);
-    const size_t block_bytes = (size_t)env_int("BIDMAT_B200_COLBLOCK_MB", 64) << 20;
+    size_t l2_bytes = 96u << 20;
+    {
+        int dev = 0, l2 = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev) == cudaSuccess && l2 > 0)
+            l2_bytes = (size_t)l2;
+    }
+    // block = half of L2 unless BIDMAT_B200_COLBLOCK_MB says otherwise (0 disables);
+    // an operand up to 1.5 x L2 is left in one piece (measured: splitting a 128 MB
+    // operand in two costs more in extra output passes than it gains in hits).
+    const int block_mb = env_int("BIDMAT_B200_COLBLOCK_MB", -1);
+    const size_t block_bytes = block_mb >= 0 ? ((size_t)block_mb << 20) : l2_bytes / 2;
     int colshift = 31;
     const int forced_cols = env_int("BIDMAT_B200_COLBLOCK_COLS", 0);   // tests force tiny blocks
     if (forced_cols > 0) {
         colshift = 0;
         while ((2 << colshift) <= forced_cols) colshift++;
-    } else if (block_bytes > 0 && dense_bytes > block_bytes + block_bytes / 2) {
+    } else if (block_bytes > 0 && dense_bytes > l2_bytes + l2_bytes / 2) {
+        // columns per block: the power of two nearest to block_bytes / column bytes
         size_t cols_per_block = block_bytes / ((size_t)nrows * sizeof(float));
         colshift = 0;
         while ((2ull << colshift) <= cols_per_block) colshift++;
+        if (cols_per_block * 1000 >= (1ull << colshift) * 1414) colshift++;
     }
 
     const int ntiles = (int)((n + kSortTile - 1) / kSortTile);

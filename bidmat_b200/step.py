@@ -74,16 +74,34 @@ class PathStep:
         _ck(_L.bidmat_b200_dds_async(self.k, S.nnz, self.A.data_ptr(), self.B.data_ptr(), S.ir.data_ptr(),
                                      S.ic.data_ptr(), self.P.data_ptr(), self.stream.cuda_stream), "dds")
 
-    def dsmultT(self):
+    def dsmultT_local(self):
+        """This rank's partial of B*^S over its column shard (no communication)."""
         S = self.S
         self.G.zero_()   # GMat.GSMultT clears the output (GMat.scala:1082)
         _ck(_L.bidmat_b200_dsmultT_async(self.k, S.n, S.nnz, self.B.data_ptr(), S.data.data_ptr(), S.ir.data_ptr(),
                                          S.ic.data_ptr(), self.G.data_ptr(), S.m, self.stream.cuda_stream), "dsmultT")
-        if self.group is not None:
-            import torch.distributed as dist
-            dist.all_reduce(self.G, op=dist.ReduceOp.SUM, group=self.group)
+
+    def allreduce_start(self):
+        """Starts the sum of the partials over ranks on NCCL's own stream; the
+        caller's stream is free to run A*S and DDS meanwhile."""
+        if self.group is None:
+            return None
+        import torch.distributed as dist
+        return dist.all_reduce(self.G, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+
+    def dsmultT(self):
+        self.dsmultT_local()
+        work = self.allreduce_start()
+        if work is not None:
+            work.wait()
 
     def run(self):
+        """One pass of the path.  The three operations are independent, so the
+        transposed product goes first and its allreduce over NVLink overlaps
+        A*S and DDS; the step ends when the reduced G is complete."""
+        self.dsmultT_local()
+        work = self.allreduce_start()
         self.dsmult()
         self.dds()
-        self.dsmultT()
+        if work is not None:
+            work.wait()
