@@ -34,6 +34,11 @@ METRIC = "nnz*k GFLOP/s over A*S + DDS + B*^S (2*k*nnz flops per operation)"
 UNIT = "GFLOP/s"
 FALLBACK_HBM_GBS = 6650.0
 
+# dram__bytes_read.sum + dram__bytes_write.sum per step from a one-pass ncu capture of the
+# default workload (seed 0, full size, one GPU); see profiles/path_kernels_config2_full_dram_traffic.md.
+# Reported only when the run is that workload.
+MEASURED_DRAM_TRAFFIC = {"dsmult": 31.25e9, "dds": 30.50e9, "dsmultT": 31.75e9}
+
 
 def parse_args():
     ap = argparse.ArgumentParser()
@@ -350,7 +355,11 @@ def run_b200(args, rank, local_rank, world):
     roofline = {"bound": "hbm", "kernel": roof_ops[dom]["kernel"], "op": dom,
                 "achieved": roof_ops[dom]["achieved_gbs"], "peak": peak, "unit": "GB/s",
                 "frac": roof_ops[dom]["frac"], "peak_source": peak_src,
-                "traffic": None, "ops": roof_ops, "kernels": kern}
+                "traffic": (MEASURED_DRAM_TRAFFIC[dom] if (world == 1 and args.scale == 1.0 and args.seed == 0
+                                                          and not args.emulate_shard) else None),
+                "traffic_note": "DRAM bytes per step of this operation's gather kernels, one-pass ncu capture of "
+                                "this workload (profiles/path_kernels_config2_full_dram_traffic.md)",
+                "ops": roof_ops, "kernels": kern}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
