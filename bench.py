@@ -170,20 +170,25 @@ def host_sample(problem, ncols):
     jc = problem.jc[:ncols + 1].cpu().numpy().astype(np.int32)
     ir = problem.ir[:j1].cpu().numpy()
     data = problem.data[:j1].cpu().numpy()
-    A = problem.A.cpu().numpy()
+    if getattr(problem, "_A_host", None) is None:
+        problem._A_host = problem.A.cpu().numpy()      # 1 GB at full size: copy once
+    A = problem._A_host
     B = problem.B[:ncols].cpu().numpy()
     return (A, B, jc, ir, data, problem.m), j1
 
 
 def calibrated_sample(problem, target_seconds, threads):
-    """Picks a column count whose three CPU loops take about `target_seconds`."""
-    probe_cols = max(64, min(problem.n, 2000))
-    sample, nnz = host_sample(problem, probe_cols)
-    t = sum(cpu_sample_run(sample, threads).values())
-    rate = max(nnz, 1) / max(t, 1e-6)                 # nonzeros per second over the three loops
-    want_nnz = rate * target_seconds
+    """Picks a column count whose three CPU loops take about `target_seconds`:
+    a probe of 20,000 columns gives the rate, one refinement corrects it."""
     avg = max(1.0, problem.nnz / problem.n)
-    ncols = int(max(probe_cols, min(problem.n, want_nnz / avg)))
+    ncols = max(64, min(problem.n, 20000))
+    for _ in range(2):
+        sample, nnz = host_sample(problem, ncols)
+        t = sum(cpu_sample_run(sample, threads).values())
+        if ncols >= problem.n or 0.6 * target_seconds <= t <= 1.5 * target_seconds:
+            break
+        rate = max(nnz, 1) / max(t, 1e-6)             # nonzeros per second over the three loops
+        ncols = int(max(64, min(problem.n, rate * target_seconds / avg)))
     return host_sample(problem, ncols) + (ncols,)
 
 

@@ -306,6 +306,19 @@ int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, con
         colshift++;
         nblocks = ((ncols - 1) >> colshift) + 1;
     }
+    // Is splitting worth it?  Unsplit, about every gather misses L2: nnz*4k bytes of
+    // DRAM reads.  Split, B is read once but every block re-reads and re-writes the
+    // output rows it touches (at most all 2^rowbits of them) and the sort may need
+    // one more pass over 24 bytes per nonzero.  Split only for a clear win; tests
+    // that force a block size skip the model.
+    if (nblocks > 1 && forced_cols <= 0) {
+        const double colbytes = 4.0 * nrows;
+        const double rows = (m_hint > 0) ? (double)m_hint : (double)(1ull << rowbits);
+        const double unsplit = (double)nnz * colbytes;
+        const int extra_pass = ((rowbits + ceil_log2((unsigned long long)nblocks) + 7) / 8) - ((rowbits + 7) / 8);
+        const double split = (double)dense_bytes + (double)nblocks * rows * 2.0 * colbytes + 48.0 * nnz * extra_pass;
+        if (split > 0.6 * unsplit) nblocks = 1;
+    }
     if (nblocks <= 1) { colshift = 31; nblocks = 1; }
     const int keybits = rowbits + (nblocks > 1 ? ceil_log2((unsigned long long)nblocks) : 0);
     const int passes = (keybits + 7) / 8;
