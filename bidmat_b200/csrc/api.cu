@@ -190,6 +190,63 @@ cudaError_t launch_dds(int k, long long nnz, const float *A, const float *B, con
     return cudaGetLastError();
 }
 
+// Sorts the nonzero list (ir, ic, v) by key (see rowsort.cuh) in `passes` 8-bit
+// passes.  Intermediate results ping-pong between the two scratch buffer sets;
+// when out_* are given the last pass writes there.  Returns the index of the
+// scratch set holding the result, or -1 when it went to out_*.
+int run_rowsort(int nnz, int passes, SortKeySpec ks, const int *ir, const int *ic, const float *v,
+                unsigned *const keys[2], int *const cols[2], float *const vals[2], unsigned *out_keys,
+                int *out_cols, float *out_vals, int *counts, int *totals, cudaStream_t st) {
+    static std::once_flag smem_once[kMaxDevices];
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= kMaxDevices) dev = 0;
+        std::call_once(smem_once[dev], [] {
+            cudaFuncSetAttribute(sort_scatter_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem));
+            cudaFuncSetAttribute(sort_scatter_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem));
+        });
+    }
+    const int ntiles = (int)(((size_t)nnz + kSortTile - 1) / kSortTile);
+    const int tps = (ntiles + kSortScanSegs - 1) / kSortScanSegs;   // tiles per scan segment
+    int cur = 0;   // scratch set holding the output of the last pass
+    ScopedSpan sp("dsmultT_rowsort", st);
+    for (int p = 0; p < passes; p++) {
+        const int shift = 8 * p;
+        const bool to_user = (p == passes - 1) && out_keys != nullptr;
+        const int out = (p == 0) ? 0 : 1 - cur;
+        unsigned *ko = to_user ? out_keys : keys[out];
+        int *co = to_user ? out_cols : cols[out];
+        float *vo = to_user ? out_vals : vals[out];
+        {
+            ScopedSpan sp1("sort_hist", st);
+            if (p == 0) {
+                sort_hist_kernel<true><<<ntiles, kSortThreads, 0, st>>>(nnz, ntiles, shift, ks, nullptr, ir, ic, counts);
+            } else {
+                sort_hist_kernel<false><<<ntiles, kSortThreads, 0, st>>>(nnz, ntiles, shift, ks, keys[cur], nullptr, nullptr, counts);
+            }
+        }
+        {
+            ScopedSpan sp2("sort_scan", st);
+            sort_scan_kernel<<<dim3(kSortScanSegs, 256), kSortThreads, 0, st>>>(ntiles, tps, counts, totals);
+            sort_digit_base_kernel<<<1, 256, 0, st>>>(totals);
+        }
+        {
+            ScopedSpan sp3("sort_scatter", st);
+            if (p == 0) {
+                sort_scatter_kernel<true><<<ntiles, kSortThreads, sizeof(SortSmem), st>>>(
+                    nnz, ntiles, shift, ks, nullptr, ir, ic, v, counts, totals, tps, ko, co, vo);
+            } else {
+                sort_scatter_kernel<false><<<ntiles, kSortThreads, sizeof(SortSmem), st>>>(
+                    nnz, ntiles, shift, ks, keys[cur], nullptr, cols[cur], vals[cur], counts, totals, tps, ko, co, vo);
+            }
+        }
+        g_launches += 4;
+        cur = to_user ? -1 : out;
+    }
+    return cur;
+}
+
 inline cudaStream_t as_stream(bidmat_stream_t s) {
     return s ? static_cast<cudaStream_t>(s) : cudaStreamPerThread;
 }
@@ -325,51 +382,8 @@ int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, con
     const SortKeySpec ks{colshift, rowbits};
     const unsigned rowmask = (rowbits >= 32) ? 0xffffffffu : ((1u << rowbits) - 1u);
 
-    static std::once_flag smem_once[kMaxDevices];
-    {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        std::call_once(smem_once[dev], [] {
-            cudaFuncSetAttribute(sort_scatter_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem));
-            cudaFuncSetAttribute(sort_scatter_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem));
-        });
-    }
-
-    int cur = 0;   // buffer holding the output of the last pass
-    {
-        ScopedSpan sp("dsmultT_rowsort", st);
-        const int tps = (ntiles + kSortScanSegs - 1) / kSortScanSegs;   // tiles per scan segment
-        for (int p = 0; p < passes; p++) {
-            const int shift = 8 * p;
-            const int out = (p == 0) ? 0 : 1 - cur;
-            {
-                ScopedSpan sp1("sort_hist", st);
-                if (p == 0) {
-                    sort_hist_kernel<true><<<ntiles, kSortThreads, 0, st>>>(nnz, ntiles, shift, ks, nullptr, Bir, Bic, counts);
-                } else {
-                    sort_hist_kernel<false><<<ntiles, kSortThreads, 0, st>>>(nnz, ntiles, shift, ks, keys[cur], nullptr, nullptr, counts);
-                }
-            }
-            {
-                ScopedSpan sp2("sort_scan", st);
-                sort_scan_kernel<<<dim3(kSortScanSegs, 256), kSortThreads, 0, st>>>(ntiles, tps, counts, totals);
-                sort_digit_base_kernel<<<1, 256, 0, st>>>(totals);
-            }
-            {
-                ScopedSpan sp3("sort_scatter", st);
-                if (p == 0) {
-                    sort_scatter_kernel<true><<<ntiles, kSortThreads, sizeof(SortSmem), st>>>(
-                        nnz, ntiles, shift, ks, nullptr, Bir, Bic, Bdata, counts, totals, tps, keys[out], cols[out], vals[out]);
-                } else {
-                    sort_scatter_kernel<false><<<ntiles, kSortThreads, sizeof(SortSmem), st>>>(
-                        nnz, ntiles, shift, ks, keys[cur], nullptr, cols[cur], vals[cur], counts, totals, tps, keys[out],
-                        cols[out], vals[out]);
-                }
-            }
-            g_launches += 4;
-            cur = out;
-        }
-    }
+    const int cur = run_rowsort(nnz, passes, ks, Bir, Bic, Bdata, keys, cols, vals, nullptr, nullptr, nullptr, counts,
+                                totals, st);
     err = cudaGetLastError();
     if (err != cudaSuccess) return (int)err;
     const int *seg = reinterpret_cast<const int *>(keys[cur]);
@@ -395,6 +409,43 @@ int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, con
         if (err != cudaSuccess) return (int)err;
     }
     return 0;
+}
+
+int bidmat_b200_transpose_csc(int nrows, int ncols, int nnz, const int *ir, const int *ic, const float *data,
+                              int *t_ir, int *t_ic, int *t_jc, float *t_data, bidmat_stream_t stream) {
+    if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = as_stream(stream);
+    if (nnz == 0) {
+        if (t_jc) return (int)cudaMemsetAsync(t_jc, 0, ((size_t)nrows + 1) * sizeof(int), st);
+        return 0;
+    }
+    if (!ir || !ic || !data || !t_ir || !t_ic || !t_data || nrows == 0) return (int)cudaErrorInvalidValue;
+    const size_t n = (size_t)nnz;
+    const int ntiles = (int)((n + kSortTile - 1) / kSortTile);
+    int rowbits = ceil_log2((unsigned long long)nrows);
+    if (rowbits < 1) rowbits = 1;
+    if (rowbits > 31) return (int)cudaErrorInvalidValue;
+    const int passes = (rowbits + 7) / 8;
+    WorkspaceLease ws(6 * pad256(n * 4) + pad256((size_t)256 * ntiles * 4) + pad256(256 * kSortScanSegs * 4) + 4096, st);
+    if (ws.err != cudaSuccess) return (int)ws.err;
+    unsigned *keys[2] = {ws.take<unsigned>(n), ws.take<unsigned>(n)};
+    int *cols[2] = {ws.take<int>(n), ws.take<int>(n)};
+    float *vals[2] = {ws.take<float>(n), ws.take<float>(n)};
+    int *counts = ws.take<int>((size_t)256 * ntiles);
+    int *totals = ws.take<int>(256 * kSortScanSegs);
+    // key = old row (the new column); payload = (old column = new row, value).  The
+    // sort is stable and ic is non-decreasing, so the new rows come out ascending
+    // inside every new column, as a CSC matrix needs.
+    run_rowsort(nnz, passes, SortKeySpec{31, rowbits}, ir, ic, data, keys, cols, vals,
+                reinterpret_cast<unsigned *>(t_ic), t_ir, t_data, counts, totals, st);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return (int)err;
+    if (t_jc) {
+        compress_ic_kernel<<<(unsigned)((n + kThreads - 1) / kThreads), kThreads, 0, st>>>(nrows, nnz, t_ic, t_jc);
+        g_launches += 1;
+        err = cudaGetLastError();
+    }
+    return (int)err;
 }
 
 int bidmat_b200_dds_async(int nrows, int nnz, const float *A, const float *B, const int *Cir,

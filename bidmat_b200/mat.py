@@ -268,6 +268,19 @@ class GSMat:
         np.cumsum(np.bincount(ic, minlength=self.ncols), out=jc[1:])
         return SMat(self.nrows, self.ncols, jc, self.pir.cpu().numpy(), self.pdata.cpu().numpy())
 
+    @property
+    def t(self):
+        """GSMat.t (GSMat.scala:218-223), done on the device instead of through a
+        CPU SMat: stable sort of the nonzeros by row."""
+        out = GSMat(self.ncols, self.nrows, self.nnz, torch.empty_like(self.pir), torch.empty_like(self.pic),
+                    torch.empty(self.nrows + 1, dtype=torch.int32, device=self.device), torch.empty_like(self.pdata))
+        with torch.cuda.device(self.device):
+            err = _L.bidmat_b200_transpose_csc(self.nrows, self.ncols, self.nnz, _ptr(self.pir), _ptr(self.pic),
+                                               _ptr(self.pdata), _ptr(out.pir), _ptr(out.pic), _ptr(out.pjc),
+                                               _ptr(out.pdata), torch.cuda.current_stream().cuda_stream)
+        _check(err, "Cuda error in GSMat.t")
+        return out
+
     def colslice(self, col1, col2):
         """GSMat.colslice (GSMat.scala:77-104): columns [col1, col2) with local,
         zero-based column indices and re-based column pointers."""

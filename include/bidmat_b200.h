@@ -139,6 +139,17 @@ BIDMAT_B200_API int bidmat_b200_dsmult_noalloc(int nrows, int ncols, int nnz, co
 BIDMAT_B200_API int bidmat_b200_expand_jc(int ncols, int nnz, const int *jc, int *ic, bidmat_stream_t stream);
 BIDMAT_B200_API int bidmat_b200_compress_ic(int ncols, int nnz, const int *ic, int *jc, bidmat_stream_t stream);
 
+/* Transpose of a GSMat on the device: T = S^T, S is nrows x ncols.  Inputs are S's
+ * per-nonzero rows, per-nonzero columns (non-decreasing) and values; outputs are
+ * T's per-nonzero rows (t_ir = S's columns), per-nonzero columns (t_ic = S's rows,
+ * non-decreasing), values, and optionally T's column pointers t_jc (nrows+1
+ * entries, may be NULL).  Rows come out ascending inside every column of T.
+ * Replaces the host round trip of GSMat.t (src/main/scala/BIDMat/GSMat.scala:218-223:
+ * download, SMat.t on the CPU, upload).  Stream-ordered, uses the workspace. */
+BIDMAT_B200_API int bidmat_b200_transpose_csc(int nrows, int ncols, int nnz, const int *ir, const int *ic,
+                                              const float *data, int *t_ir, int *t_ic, int *t_jc,
+                                              float *t_data, bidmat_stream_t stream);
+
 /* Validates a GSMat structure on the device without touching values:
  * 0 <= ir < m, 0 <= ic < ncols, ic non-decreasing.  Returns 0 when it holds,
  * cudaErrorInvalidValue (1) when it does not, another cudaError_t on failure.

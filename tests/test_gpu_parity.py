@@ -268,6 +268,28 @@ def test_structure_helpers_on_device(cuda_device):
     assert L.bidmat_b200_check_structure(m, n, S.nnz, S.ir.data_ptr(), flipped.data_ptr()) == 1
 
 
+@pytest.mark.parametrize("m,n,dens", [(10, 20, 0.1), (300, 70, 0.3), (5000, 9000, 0.002), (70000, 40, 0.01)])
+def test_device_transpose_is_bit_exact(cuda_device, m, n, dens):
+    """GSMatTest "support matrix transpose" (GSMatTest.scala:47-54): aa.t against
+    the CPU transpose -- here structure and values must match bit for bit."""
+    import scipy.sparse as sp
+    from bidmat_b200.mat import GSMat, SMat
+    rng = np.random.default_rng(m + n)
+    jc, ir, data = random_csc(m, n, dens, rng, empty_cols=(0, n - 1))
+    aa = GSMat.fromSMat(SMat(m, n, jc, ir, data).check(), cuda_device)
+    bb = aa.t
+    assert (bb.nrows, bb.ncols, bb.nnz) == (n, m, len(ir))
+    out = bb.toSMat().check()
+    ref = sp.csc_matrix((data, ir, jc), shape=(m, n)).T.tocsc()
+    ref.sort_indices()
+    assert np.array_equal(out.jc, ref.indptr) and np.array_equal(out.ir, ref.indices)
+    assert np.array_equal(out.data.view(np.uint32), ref.data.astype(np.float32).view(np.uint32))
+    assert np.array_equal(bb.pjc.cpu().numpy(), ref.indptr)
+    # transposing twice gives the matrix back
+    cc = bb.t.toSMat().check()
+    assert np.array_equal(cc.jc, jc) and np.array_equal(cc.ir, ir) and np.array_equal(cc.data, data)
+
+
 def test_mirror_operators_and_errors(cuda_device):
     from bidmat_b200.mat import GMat, GSMat, Mat, SMat
     rng = np.random.default_rng(29)
