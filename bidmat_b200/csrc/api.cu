@@ -15,6 +15,7 @@
 #include "kernels.cuh"
 #include "structure_kernels.cuh"
 #include "rowsort.cuh"
+#include "edgeops.cuh"
 #include "host_common.cuh"
 
 using namespace bidmat;
@@ -554,6 +555,81 @@ int bidmat_b200_check_structure(int m, int ncols, int nnz, const int *ir, const 
     if (err == cudaSuccess) err = cudaStreamSynchronize(st);
     if (err != cudaSuccess) return (int)err;
     return h ? (int)cudaErrorInvalidValue : 0;
+}
+
+static int sdop_common(int nnz, float *A, const int *idx, const float *B, int len, int opn) {
+    if (nnz < 0 || len < 0 || opn < 0 || opn >= kNumBinops) return (int)cudaErrorInvalidValue;
+    if (nnz == 0) return 0;
+    if (!A || !B || (len > 1 && !idx)) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = cudaStreamPerThread;
+    size_t blocks = ((size_t)nnz + kThreads - 1) / kThreads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    sdop_kernel<<<(unsigned)blocks, kThreads, 0, st>>>(nnz, A, len > 1 ? idx : nullptr, B, opn);
+    g_launches += 1;
+    return finish_sync(cudaGetLastError(), st);
+}
+
+int bidmat_b200_sdoprow(int nrows, int ncols, int nnz, float *A, const int *Aic, const float *B, int len, int opn) {
+    (void)nrows; (void)ncols;
+    return sdop_common(nnz, A, Aic, B, len, opn);
+}
+
+int bidmat_b200_sdopcol(int nrows, int ncols, int nnz, float *A, const int *Air, const float *B, int len, int opn) {
+    (void)nrows; (void)ncols;
+    return sdop_common(nnz, A, Air, B, len, opn);
+}
+
+int bidmat_b200_spsum(int nrows, int ncols, int nnz, const int *Air, const int *Aic, const float *P, float *B, int n) {
+    if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (nnz == 0) return 0;
+    if (!Air || !Aic || !P || !B) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = cudaStreamPerThread;
+    // Both sums are the gather-accumulate kernel with a 1 x 1 dense operand holding
+    // 1.0: B[seg[j]] += P[j] * 1, summed without atomics in nonzero order.
+    const Shape s = pick_shape(1, false);
+    const int chunk = pick_chunk(nnz, s.lpv);
+    const size_t n_ = (size_t)nnz;
+    if (n == 1) {
+        // B(1 x ncols)[ic[j]] += P[j]: the column indices are already sorted
+        WorkspaceLease ws(pad256(n_ * 4) + pad256(ga_part_floats(1, nnz, chunk) * 4) + 1024, st);
+        if (ws.err != cudaSuccess) return (int)ws.err;
+        int *zeros = ws.take<int>(n_);
+        float *part = ws.take<float>(ga_part_floats(1, nnz, chunk));
+        float *one = ws.take<float>(1);
+        cudaError_t err = cudaMemsetAsync(zeros, 0, n_ * 4, st);
+        if (err != cudaSuccess) return (int)err;
+        fill_one_kernel<<<1, 1, 0, st>>>(one);
+        g_launches += 1;
+        err = launch_ga(1, nnz, one, P, zeros, Aic, B, part, chunk, s, st, "spsum_ga_chunk");
+        return finish_sync(err, st);
+    }
+    // B(nrows x 1)[ir[j]] += P[j]: stable sort by row first, then the same kernel
+    const int ntiles = (int)((n_ + kSortTile - 1) / kSortTile);
+    int rowbits = ceil_log2((unsigned long long)(nrows > 0 ? nrows : 1));
+    if (rowbits < 1) rowbits = 1;
+    if (rowbits > 31) return (int)cudaErrorInvalidValue;
+    WorkspaceLease ws(7 * pad256(n_ * 4) + pad256((size_t)256 * ntiles * 4) + pad256(256 * kSortScanSegs * 4) +
+                          pad256(ga_part_floats(1, nnz, chunk) * 4) + 4096, st);
+    if (ws.err != cudaSuccess) return (int)ws.err;
+    unsigned *keys[2] = {ws.take<unsigned>(n_), ws.take<unsigned>(n_)};
+    int *cols[2] = {ws.take<int>(n_), ws.take<int>(n_)};
+    float *vals[2] = {ws.take<float>(n_), ws.take<float>(n_)};
+    int *zeros = ws.take<int>(n_);
+    int *counts = ws.take<int>((size_t)256 * ntiles);
+    int *totals = ws.take<int>(256 * kSortScanSegs);
+    float *part = ws.take<float>(ga_part_floats(1, nnz, chunk));
+    float *one = ws.take<float>(1);
+    cudaError_t err = cudaMemsetAsync(zeros, 0, n_ * 4, st);
+    if (err != cudaSuccess) return (int)err;
+    fill_one_kernel<<<1, 1, 0, st>>>(one);
+    g_launches += 1;
+    const int cur = run_rowsort(nnz, (rowbits + 7) / 8, SortKeySpec{31, rowbits}, Air, Aic, P, keys, cols, vals,
+                                nullptr, nullptr, nullptr, counts, totals, st);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return (int)err;
+    err = launch_ga(1, nnz, one, vals[cur], zeros, reinterpret_cast<const int *>(keys[cur]), B, part, chunk, s, st,
+                    "spsum_ga_chunk");
+    return finish_sync(err, st);
 }
 
 long long bidmat_b200_workspace_bytes(void) {

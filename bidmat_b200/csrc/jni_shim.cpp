@@ -91,6 +91,30 @@ JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_dsmultxtune(JNIEnv *env, jcla
     return Java_edu_berkeley_bid_CUMAT_dsmult(env, c, nrows, ncols, nnz, jA, jBdata, jBir, jBic, jC);
 }
 
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_spsum(JNIEnv *env, jclass, jint nrows, jint ncols, jint nnz,
+                                                        jobject jAir, jobject jAic, jobject jP, jobject jB, jint n) {
+    if (!init_field_ids(env)) return 1;
+    return bidmat_b200_spsum(nrows, ncols, nnz, (const int *)device_address(env, jAir),
+                             (const int *)device_address(env, jAic), (const float *)device_address(env, jP),
+                             (float *)device_address(env, jB), n);
+}
+
+// Rebinding these two also captures BIDMat's double-precision overloads of the same
+// Java methods; only bind them when GSDMat edge operators are not in use.
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_sdoprow(JNIEnv *env, jclass, jint nrows, jint ncols, jint nnz,
+                                                          jobject jA, jobject jAic, jobject jB, jint len, jint opn) {
+    if (!init_field_ids(env)) return 1;
+    return bidmat_b200_sdoprow(nrows, ncols, nnz, (float *)device_address(env, jA),
+                               (const int *)device_address(env, jAic), (const float *)device_address(env, jB), len, opn);
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_sdopcol(JNIEnv *env, jclass, jint nrows, jint ncols, jint nnz,
+                                                          jobject jA, jobject jAir, jobject jB, jint len, jint opn) {
+    if (!init_field_ids(env)) return 1;
+    return bidmat_b200_sdopcol(nrows, ncols, nnz, (float *)device_address(env, jA),
+                               (const int *)device_address(env, jAir), (const float *)device_address(env, jB), len, opn);
+}
+
 // Route (ii): rebind the four natives when this library is loaded by System.load.
 JNIEXPORT jint JNICALL JNI_OnLoad(JavaVM *vm, void *) {
     JNIEnv *env = nullptr;

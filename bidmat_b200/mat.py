@@ -281,6 +281,53 @@ class GSMat:
         _check(err, "Cuda error in GSMat.t")
         return out
 
+    def copy(self):
+        return GSMat(self.nrows, self.ncols, self.nnz, self.pir.clone(), self.pic.clone(), self.pjc.clone(),
+                     self.pdata.clone())
+
+    def sum(self, n=0):
+        """GSMat.sum (GSMat.scala:250-261): n == 1 column sums (1 x ncols), n == 2
+        row sums (nrows x 1); n == 0 picks 2 for a single-row matrix, else 1."""
+        nn = n if n > 0 else (2 if self.nrows == 1 else 1)
+        out = GMat.zeros(1 if nn == 1 else self.nrows, self.ncols if nn == 1 else 1, self.device)
+        Mat.nflops += self.nnz
+        err = _L.bidmat_b200_spsum(self.nrows, self.ncols, self.nnz, _ptr(self.pir), _ptr(self.pic), _ptr(self.pdata),
+                                   out.pdata, nn)
+        _check(err, "Cuda error in GSMAT.sum")
+        return out
+
+    def GSDop(self, b, op):
+        """GSMat.GSDop (GSMat.scala:315-330): combine every stored value with the
+        entry of a row vector (1 x ncols), a column vector (nrows x 1) or a scalar."""
+        if b.nrows > 1 and b.ncols > 1:
+            raise RuntimeError("Sorry only edge operators supported for GSMat op GMat")
+        length = b.nrows * b.ncols
+        if b.nrows != self.nrows and b.ncols != self.ncols and length > 1:
+            raise RuntimeError("GSMat op GMat: dimensions mismatch")
+        Mat.nflops += self.nnz
+        out = self.copy()
+        if b.ncols > 1:
+            err = _L.bidmat_b200_sdoprow(self.nrows, self.ncols, self.nnz, _ptr(out.pdata), _ptr(out.pic), b.pdata,
+                                         length, op)
+        else:
+            err = _L.bidmat_b200_sdopcol(self.nrows, self.ncols, self.nnz, _ptr(out.pdata), _ptr(out.pir), b.pdata,
+                                         length, op)
+        _check(err, "Cuda error in GSMat op GMat")
+        return out
+
+    def __add__(self, b):
+        return self.GSDop(b, 0)
+
+    def __sub__(self, b):
+        return self.GSDop(b, 1)
+
+    def mul_at(self, b):
+        """`S *@ v` (element-wise product with an edge vector)."""
+        return self.GSDop(b, 2)
+
+    def __truediv__(self, b):
+        return self.GSDop(b, 3)
+
     def colslice(self, col1, col2):
         """GSMat.colslice (GSMat.scala:77-104): columns [col1, col2) with local,
         zero-based column indices and re-based column pointers."""

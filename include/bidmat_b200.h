@@ -150,6 +150,27 @@ BIDMAT_B200_API int bidmat_b200_transpose_csc(int nrows, int ncols, int nnz, con
                                               const float *data, int *t_ir, int *t_ic, int *t_jc,
                                               float *t_data, bidmat_stream_t stream);
 
+/* Edge operators on the values of a GSMat: A[j] = op(A[j], B[Aic[j]]) (sdoprow, B is
+ * a 1 x ncols row) or op(A[j], B[Air[j]]) (sdopcol, B is an nrows x 1 column); with
+ * len == 1 every value is combined with B[0].  opn indexes BIDMat's operator table
+ * (0 add, 1 sub, 2 mul, 3 div, 4 gt, 5 lt, 6 eq, 7 ge, 8 le, 9 ne, 10 max, 11 min,
+ * 12 atan2, 13 pow, 14 ifpos; jni/src/Operators.cu:86-101).  Synchronous.
+ * Replaces: sdoprow / sdopcol (jni/include/MatKernel.hpp:47,51,
+ *   jni/src/Operators.cu:586-644, CUMAT.java:135,139, BIDMat_CUMAT.cpp:252-293). */
+BIDMAT_B200_API int bidmat_b200_sdoprow(int nrows, int ncols, int nnz, float *A, const int *Aic, const float *B,
+                                        int len, int opn);
+BIDMAT_B200_API int bidmat_b200_sdopcol(int nrows, int ncols, int nnz, float *A, const int *Air, const float *B,
+                                        int len, int opn);
+
+/* Sums of the values of a GSMat: n == 1: B(1 x ncols)[Aic[j]] += P[j] (column sums);
+ * otherwise B(nrows x 1)[Air[j]] += P[j] (row sums).  Accumulates, without float
+ * atomics (the reference adds with atomicAdd), so the result is bit-reproducible.
+ * Synchronous.
+ * Replaces: spsum (jni/include/MatKernel.hpp:152, jni/src/Arith.cu:250-277,
+ *   CUMAT.java:209, BIDMat_CUMAT.cpp:873-881). */
+BIDMAT_B200_API int bidmat_b200_spsum(int nrows, int ncols, int nnz, const int *Air, const int *Aic,
+                                      const float *P, float *B, int n);
+
 /* Validates a GSMat structure on the device without touching values:
  * 0 <= ir < m, 0 <= ic < ncols, ic non-decreasing.  Returns 0 when it holds,
  * cudaErrorInvalidValue (1) when it does not, another cudaError_t on failure.
