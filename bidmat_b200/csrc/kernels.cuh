@@ -214,8 +214,8 @@ template <int LPV> __device__ __forceinline__ void worker_sync(unsigned mask) {
     __syncwarp(mask);
 }
 
-template <int LPV, int NT, int U, int TPB>
-__global__ void __launch_bounds__(TPB)
+template <int LPV, int NT, int U, int TPB, int MINB = 1>
+__global__ void __launch_bounds__(TPB, MINB)
 ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
                      const float *__restrict__ D, const float *__restrict__ val,
                      const int *__restrict__ gidx, const int *__restrict__ seg,
