@@ -35,7 +35,7 @@ UNIT = "GFLOP/s"
 FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per step from a one-pass ncu capture of the
-# default workload (seed 0, full size, one GPU); see profiles/path_kernels_config2_full_dram_traffic.md.
+# default workload (seed 0, full size, one GPU); the capture's summary is committed under profiles/.
 # Reported only when the run is that workload.
 MEASURED_DRAM_TRAFFIC = {"dsmult": 31.25e9, "dds": 30.50e9, "dsmultT": 31.75e9}
 
@@ -363,7 +363,7 @@ def run_b200(args, rank, local_rank, world):
                 "traffic": (MEASURED_DRAM_TRAFFIC[dom] if (world == 1 and args.scale == 1.0 and args.seed == 0
                                                           and not args.emulate_shard) else None),
                 "traffic_note": "DRAM bytes per step of this operation's gather kernels, one-pass ncu capture of "
-                                "this workload (profiles/path_kernels_config2_full_dram_traffic.md)",
+                                "this workload (summary committed under profiles/)",
                 "ops": roof_ops, "kernels": kern}
 
     line = {
