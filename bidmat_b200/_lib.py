@@ -24,6 +24,13 @@ _SIGNATURES = {
     "bidmat_b200_dsmultx_tune": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),
     "bidmat_b200_dsmult_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dsmultT_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _c_int, _vp]),
+    "bidmat_b200_dsmult_f64": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp]),
+    "bidmat_b200_dsmultT_f64": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp]),
+    "bidmat_b200_dds_f64": (_c_int, [_c_int, _c_int, _vp, _vp, _vp, _vp, _vp]),
+    "bidmat_b200_dds0_f64": (_c_int, [_c_int, _c_int, _vp, _vp, _vp, _vp, _vp]),
+    "bidmat_b200_dsmult_f64_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "bidmat_b200_dsmultT_f64_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _c_int, _vp]),
+    "bidmat_b200_dds_f64_async": (_c_int, [_c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dsmult_noalloc": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dds_async": (_c_int, [_c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dds0_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 #include <vector>
 
 #include "../../include/bidmat_b200.h"
@@ -120,38 +121,46 @@ bool fast_shape(int k, const Shape &s) { return s.vec == 4 && s.tiles == 1 && k 
 
 // `count` nonzeros are processed: the whole list (range == nullptr, count == nnz) or
 // the slice [range[0], range[1]) read on the device.  The output column of a
-// nonzero is seg & segmask.
-cudaError_t launch_ga(int k, long long nnz, const float *D, const float *val, const int *gidx,
-                      const int *seg, float *O, float *part, int chunk, const Shape &s,
+// nonzero is seg & segmask.  S is float or double; the predicate-free fast
+// kernels exist for float only.
+template <typename S>
+cudaError_t launch_ga(int k, long long nnz, const S *D, const S *val, const int *gidx,
+                      const int *seg, S *O, S *part, int chunk, const Shape &s,
                       cudaStream_t st, const char *label, long long count = -1,
                       const int *range = nullptr, unsigned segmask = 0xffffffffu) {
+    constexpr int kWideVec = 16 / (int)sizeof(S);
     if (count < 0) count = nnz;
     if (count == 0) return cudaSuccess;
     const long long nchunks = (count + chunk - 1) / chunk;
     dim3 grid(blocks_for(nchunks, s.lpv), s.tiles, 1);
-    if (fast_shape(k, s) && !env_int("BIDMAT_B200_GENERIC", 0)) {
-        const int wpb = kFastThreads / s.lpv;
-        dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
-        ScopedSpan sp(label, st);
+    bool done = false;
+    if constexpr (std::is_same<S, float>::value) {
+        if (fast_shape(k, s) && !env_int("BIDMAT_B200_GENERIC", 0)) {
+            const int wpb = kFastThreads / s.lpv;
+            dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
+            ScopedSpan sp(label, st);
 #define CALL_FAST(LPV, NT, U, MINB)                                                                    \
     ga_chunk_fast_kernel<LPV, NT, U, kFastThreads, MINB><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, D, val, \
                                                                                         gidx, seg, O, part, range, segmask)
-        // k = 256: five CTAs of 128 threads per SM (<= 96 registers) measured 10 % faster
-        // than the 118-register build at four; for the other heights the register cap
-        // costs more in spills than the extra CTA gains (measured at k = 128).
-        if (s.lpv == 8) CALL_FAST(8, 1, 4, 1);
-        else if (s.lpv == 16) CALL_FAST(16, 1, 4, 1);
-        else if (s.nt == 1) CALL_FAST(32, 1, 4, 1);
-        else if (s.nt == 2) CALL_FAST(32, 2, 2, 5);
-        else CALL_FAST(32, 4, 1, 1);
+            // k = 256: five CTAs of 128 threads per SM (<= 96 registers) measured 10 % faster
+            // than the 118-register build at four; for the other heights the register cap
+            // costs more in spills than the extra CTA gains (measured at k = 128).
+            if (s.lpv == 8) CALL_FAST(8, 1, 4, 1);
+            else if (s.lpv == 16) CALL_FAST(16, 1, 4, 1);
+            else if (s.nt == 1) CALL_FAST(32, 1, 4, 1);
+            else if (s.nt == 2) CALL_FAST(32, 2, 2, 5);
+            else CALL_FAST(32, 4, 1, 1);
 #undef CALL_FAST
-    } else {
+            done = true;
+        }
+    }
+    if (!done) {
 #define CALL_GA(VEC, LPV, NT)                                                                   \
     {                                                                                           \
         ScopedSpan sp(label, st);                                                               \
-        ga_chunk_kernel<VEC, LPV, NT, 4><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, D, val, \
-                                                                    gidx, seg, O, part, range,  \
-                                                                    segmask);                   \
+        ga_chunk_kernel<S, VEC, LPV, NT, 4><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, D, val, \
+                                                                       gidx, seg, O, part, range, \
+                                                                       segmask);                \
     }
         DISPATCH_SHAPE(s, CALL_GA);
 #undef CALL_GA
@@ -159,7 +168,7 @@ cudaError_t launch_ga(int k, long long nnz, const float *D, const float *val, co
     if (nchunks > 1) {
         ScopedSpan sp("ga_fixup", st);
 #define CALL_FIX(VEC, LPV, NT) \
-    ga_fixup_kernel<VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, seg, O, part, range, segmask);
+    ga_fixup_kernel<S, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, seg, O, part, range, segmask);
         DISPATCH_SHAPE(s, CALL_FIX);
 #undef CALL_FIX
     }
@@ -167,25 +176,31 @@ cudaError_t launch_ga(int k, long long nnz, const float *D, const float *val, co
     return cudaGetLastError();
 }
 
-template <bool ACCUM>
-cudaError_t launch_dds(int k, long long nnz, const float *A, const float *B, const int *ir,
-                       const int *ic, float *P, cudaStream_t st) {
-    const Shape s = pick_shape(k, is16(A) && is16(B));
+template <typename S, bool ACCUM>
+cudaError_t launch_dds(int k, long long nnz, const S *A, const S *B, const int *ir,
+                       const int *ic, S *P, cudaStream_t st) {
+    constexpr int kWideVec = 16 / (int)sizeof(S);
+    const Shape s = pick_shape(k, is16(A) && is16(B), kWideVec);
     const int chunk = pick_chunk(nnz, s.lpv);
     const long long nchunks = (nnz + chunk - 1) / chunk;
     dim3 grid(blocks_for(nchunks, s.lpv), 1, 1);
     ScopedSpan sp("dds_chunk", st);
-    if (fast_shape(k, s) && s.lpv == 32 && s.nt <= 2 && !env_int("BIDMAT_B200_GENERIC", 0)) {
-        const int wpb = kFastThreads / 32;
-        dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
-        if (s.nt == 1)
-            dds_chunk_fast_kernel<1, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
-        else
-            dds_chunk_fast_kernel<2, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
-    } else {
+    bool done = false;
+    if constexpr (std::is_same<S, float>::value) {
+        if (fast_shape(k, s) && s.lpv == 32 && s.nt <= 2 && !env_int("BIDMAT_B200_GENERIC", 0)) {
+            const int wpb = kFastThreads / 32;
+            dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
+            if (s.nt == 1)
+                dds_chunk_fast_kernel<1, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
+            else
+                dds_chunk_fast_kernel<2, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
+            done = true;
+        }
+    }
+    if (!done) {
 #define CALL_DDS(VEC, LPV, NT)                                                                  \
-    dds_chunk_kernel<VEC, LPV, NT, 4, ACCUM><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, A, B, \
-                                                                        ir, ic, P);
+    dds_chunk_kernel<S, VEC, LPV, NT, 4, ACCUM><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, A, B, \
+                                                                           ir, ic, P);
         DISPATCH_SHAPE(s, CALL_DDS);
 #undef CALL_DDS
     }
@@ -197,17 +212,18 @@ cudaError_t launch_dds(int k, long long nnz, const float *A, const float *B, con
 // passes.  Intermediate results ping-pong between the two scratch buffer sets;
 // when out_* are given the last pass writes there.  Returns the index of the
 // scratch set holding the result, or -1 when it went to out_*.
-int run_rowsort(int nnz, int passes, SortKeySpec ks, const int *ir, const int *ic, const float *v,
-                unsigned *const keys[2], int *const cols[2], float *const vals[2], unsigned *out_keys,
-                int *out_cols, float *out_vals, int *counts, int *totals, cudaStream_t st) {
+template <typename S>
+int run_rowsort(int nnz, int passes, SortKeySpec ks, const int *ir, const int *ic, const S *v,
+                unsigned *const keys[2], int *const cols[2], S *const vals[2], unsigned *out_keys,
+                int *out_cols, S *out_vals, int *counts, int *totals, cudaStream_t st) {
     static std::once_flag smem_once[kMaxDevices];
     {
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev < 0 || dev >= kMaxDevices) dev = 0;
         std::call_once(smem_once[dev], [] {
-            cudaFuncSetAttribute(sort_scatter_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem));
-            cudaFuncSetAttribute(sort_scatter_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem));
+            cudaFuncSetAttribute(sort_scatter_kernel<true, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem<S>));
+            cudaFuncSetAttribute(sort_scatter_kernel<false, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem<S>));
         });
     }
     const int ntiles = (int)(((size_t)nnz + kSortTile - 1) / kSortTile);
@@ -220,7 +236,7 @@ int run_rowsort(int nnz, int passes, SortKeySpec ks, const int *ir, const int *i
         const int out = (p == 0) ? 0 : 1 - cur;
         unsigned *ko = to_user ? out_keys : keys[out];
         int *co = to_user ? out_cols : cols[out];
-        float *vo = to_user ? out_vals : vals[out];
+        S *vo = to_user ? out_vals : vals[out];
         {
             ScopedSpan sp1("sort_hist", st);
             if (p == 0) {
@@ -237,10 +253,10 @@ int run_rowsort(int nnz, int passes, SortKeySpec ks, const int *ir, const int *i
         {
             ScopedSpan sp3("sort_scatter", st);
             if (p == 0) {
-                sort_scatter_kernel<true><<<ntiles, kSortThreads, sizeof(SortSmem), st>>>(
+                sort_scatter_kernel<true, S><<<ntiles, kSortThreads, sizeof(SortSmem<S>), st>>>(
                     nnz, ntiles, shift, ks, nullptr, ir, ic, v, counts, totals, tps, ko, co, vo);
             } else {
-                sort_scatter_kernel<false><<<ntiles, kSortThreads, sizeof(SortSmem), st>>>(
+                sort_scatter_kernel<false, S><<<ntiles, kSortThreads, sizeof(SortSmem<S>), st>>>(
                     nnz, ntiles, shift, ks, keys[cur], nullptr, cols[cur], vals[cur], counts, totals, tps, ko, co, vo);
             }
         }
@@ -267,38 +283,36 @@ int ceil_log2(unsigned long long v) {  // smallest b with 2^b >= v (v >= 1)
     return b;
 }
 
-}  // namespace
-
-extern "C" {
-
-int bidmat_b200_dsmult_async(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
-                             const int *Bir, const int *Bic, float *C, bidmat_stream_t stream) {
+template <typename S>
+int dsmult_impl(int nrows, int ncols, int nnz, const S *A, const S *Bdata,
+                             const int *Bir, const int *Bic, S *C, cudaStream_t st_in) {
     if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
     if (nnz == 0 || nrows == 0) return 0;
     if (!A || !Bdata || !Bir || !Bic || !C) return (int)cudaErrorInvalidValue;
-    cudaStream_t st = as_stream(stream);
-    const Shape s = pick_shape(nrows, is16(A) && is16(C));
+    cudaStream_t st = st_in;
+    const Shape s = pick_shape(nrows, is16(A) && is16(C), 16 / (int)sizeof(S));
     const int chunk = pick_chunk(nnz, s.lpv);
-    WorkspaceLease ws(pad256(ga_part_floats(nrows, nnz, chunk) * sizeof(float)) + 256, st);
+    WorkspaceLease ws(pad256(ga_part_floats(nrows, nnz, chunk) * sizeof(S)) + 256, st);
     if (ws.err != cudaSuccess) return (int)ws.err;
-    float *part = ws.take<float>(ga_part_floats(nrows, nnz, chunk));
-    return (int)launch_ga(nrows, nnz, A, Bdata, Bir, Bic, C, part, chunk, s, st, "dsmult_ga_chunk");
+    S *part = ws.take<S>(ga_part_floats(nrows, nnz, chunk));
+    return (int)launch_ga<S>(nrows, nnz, A, Bdata, Bir, Bic, C, part, chunk, s, st, "dsmult_ga_chunk");
 }
 
-int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
-                              const int *Bir, const int *Bic, float *C, int m_hint,
-                              bidmat_stream_t stream) {
+template <typename S>
+int dsmultT_impl(int nrows, int ncols, int nnz, const S *A, const S *Bdata,
+                              const int *Bir, const int *Bic, S *C, int m_hint,
+                              cudaStream_t st_in) {
     if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
     if (nnz == 0 || nrows == 0) return 0;
     if (!A || !Bdata || !Bir || !Bic || !C) return (int)cudaErrorInvalidValue;
-    cudaStream_t st = as_stream(stream);
+    cudaStream_t st = st_in;
     const size_t n = (size_t)nnz;
-    const Shape s = pick_shape(nrows, is16(A) && is16(C));
+    const Shape s = pick_shape(nrows, is16(A) && is16(C), 16 / (int)sizeof(S));
 
     // Column blocks: when the dense operand is much larger than L2, the nonzeros
     // are ordered by (column block, row) so that the gathers of one block stay
     // L2-resident; blocks are then processed one after the other.
-    const size_t dense_bytes = (size_t)ncols * (size_t)nrows * sizeof(float);
+    const size_t dense_bytes = (size_t)ncols * (size_t)nrows * sizeof(S);
     size_t l2_bytes = 96u << 20;
     {
         int dev = 0, l2 = 0;
@@ -318,30 +332,30 @@ int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, con
         while ((2 << colshift) <= forced_cols) colshift++;
     } else if (block_bytes > 0 && dense_bytes > l2_bytes + l2_bytes / 2) {
         // columns per block: the power of two nearest to block_bytes / column bytes
-        size_t cols_per_block = block_bytes / ((size_t)nrows * sizeof(float));
+        size_t cols_per_block = block_bytes / ((size_t)nrows * sizeof(S));
         colshift = 0;
         while ((2ull << colshift) <= cols_per_block) colshift++;
         if (cols_per_block * 1000 >= (1ull << colshift) * 1414) colshift++;
     }
 
     const int ntiles = (int)((n + kSortTile - 1) / kSortTile);
-    size_t need = 6 * pad256(n * 4) + pad256((size_t)256 * ntiles * 4) + 4 * pad256(4096) + pad256(256 * kSortScanSegs * 4) + 4096;
+    size_t need = 4 * pad256(n * 4) + 2 * pad256(n * sizeof(S)) + pad256((size_t)256 * ntiles * 4) + 4 * pad256(4096) + pad256(256 * kSortScanSegs * 4) + 4096;
     // Partial-sum scratch: enough chunk slots for the whole list or for any single
     // column block, whichever chunk length pick_chunk gives them.
     const int chunk_all = pick_chunk(nnz, s.lpv);
     const long long cap_chunks = max_chunks_for(nnz, s.lpv);
     const size_t part_floats = (size_t)cap_chunks * 2 * (size_t)nrows;
-    need += pad256(part_floats * 4);
+    need += pad256(part_floats * sizeof(S));
     WorkspaceLease ws(need, st);
     if (ws.err != cudaSuccess) return (int)ws.err;
     unsigned *keys[2] = {ws.take<unsigned>(n), ws.take<unsigned>(n)};
     int *cols[2] = {ws.take<int>(n), ws.take<int>(n)};
-    float *vals[2] = {ws.take<float>(n), ws.take<float>(n)};
+    S *vals[2] = {ws.take<S>(n), ws.take<S>(n)};
     int *counts = ws.take<int>((size_t)256 * ntiles);
     int *totals = ws.take<int>(256 * kSortScanSegs);   // per (digit, scan segment)
     int *maxrow = ws.take<int>(1);
     int *offsets = ws.take<int>(1024);
-    float *part = ws.take<float>(part_floats);
+    S *part = ws.take<S>(part_floats);
 
     cudaError_t err;
     int rowbits;
@@ -372,11 +386,12 @@ int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, con
     // one more pass over 24 bytes per nonzero.  Split only for a clear win; tests
     // that force a block size skip the model.
     if (nblocks > 1 && forced_cols <= 0) {
-        const double colbytes = 4.0 * nrows;
+        const double colbytes = (double)sizeof(S) * nrows;
         const double rows = (m_hint > 0) ? (double)m_hint : (double)(1ull << rowbits);
         const double unsplit = (double)nnz * colbytes;
         const int extra_pass = ((rowbits + ceil_log2((unsigned long long)nblocks) + 7) / 8) - ((rowbits + 7) / 8);
-        const double split = (double)dense_bytes + (double)nblocks * rows * 2.0 * colbytes + 48.0 * nnz * extra_pass;
+        const double split = (double)dense_bytes + (double)nblocks * rows * 2.0 * colbytes +
+                             2.0 * (8.0 + sizeof(S)) * nnz * extra_pass;
         if (split > 0.6 * unsplit) nblocks = 1;
     }
     if (nblocks <= 1) { colshift = 31; nblocks = 1; }
@@ -385,14 +400,14 @@ int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, con
     const SortKeySpec ks{colshift, rowbits};
     const unsigned rowmask = (rowbits >= 32) ? 0xffffffffu : ((1u << rowbits) - 1u);
 
-    const int cur = run_rowsort(nnz, passes, ks, Bir, Bic, Bdata, keys, cols, vals, nullptr, nullptr, nullptr, counts,
+    const int cur = run_rowsort<S>(nnz, passes, ks, Bir, Bic, Bdata, keys, cols, vals, nullptr, nullptr, nullptr, counts,
                                 totals, st);
     err = cudaGetLastError();
     if (err != cudaSuccess) return (int)err;
     const int *seg = reinterpret_cast<const int *>(keys[cur]);
 
     if (nblocks == 1) {
-        return (int)launch_ga(nrows, nnz, A, vals[cur], cols[cur], seg, C, part, chunk_all, s, st, "dsmultT_ga_chunk",
+        return (int)launch_ga<S>(nrows, nnz, A, vals[cur], cols[cur], seg, C, part, chunk_all, s, st, "dsmultT_ga_chunk",
                               nnz, nullptr, rowmask);
     }
     // slice boundaries of the column blocks in the sorted list
@@ -407,11 +422,64 @@ int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, con
         if (count <= 0) continue;
         int chunk = pick_chunk(count, s.lpv);
         if (ga_part_floats(nrows, count, chunk) > part_floats) chunk = chunk_all;
-        err = launch_ga(nrows, nnz, A, vals[cur], cols[cur], seg, C, part, chunk, s, st, "dsmultT_ga_chunk", count,
+        err = launch_ga<S>(nrows, nnz, A, vals[cur], cols[cur], seg, C, part, chunk, s, st, "dsmultT_ga_chunk", count,
                         offsets + b, rowmask);
         if (err != cudaSuccess) return (int)err;
     }
     return 0;
+}
+
+template <typename S>
+int dds_impl(int nrows, int nnz, const S *A, const S *B, const int *Cir,
+                          const int *Cic, S *P, cudaStream_t st_in) {
+    if (nrows < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (nnz == 0) return 0;
+    if (!A || !B || !Cir || !Cic || !P) return (int)cudaErrorInvalidValue;
+    if (nrows == 0) return 0;
+    return (int)launch_dds<S, true>(nrows, nnz, A, B, Cir, Cic, P, st_in);
+}
+
+template <typename S>
+int dds0_impl(int nrows, int ncols, int nnz, const S *A, const S *B,
+                           const int *Cir, const int *Cjc, S *P, cudaStream_t st_in) {
+    if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (nnz == 0 || ncols == 0) return 0;
+    if (!A || !B || !Cir || !Cjc || !P) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = st_in;
+    if (nrows == 0) return (int)cudaMemsetAsync(P, 0, (size_t)nnz * sizeof(S), st);
+    WorkspaceLease ws(pad256((size_t)nnz * 4) + 256, st);
+    if (ws.err != cudaSuccess) return (int)ws.err;
+    int *ic = ws.take<int>((size_t)nnz);
+    expand_jc_kernel<<<(unsigned)(((size_t)nnz + kThreads - 1) / kThreads), kThreads, 0, st>>>(ncols, nnz, Cjc, ic);
+    g_launches += 1;
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return (int)err;
+    return (int)launch_dds<S, false>(nrows, nnz, A, B, Cir, ic, P, st);
+}
+
+}  // namespace
+
+extern "C" {
+
+int bidmat_b200_dsmult_async(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                             const int *Bir, const int *Bic, float *C, bidmat_stream_t stream) {
+    return dsmult_impl<float>(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, as_stream(stream));
+}
+
+int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
+                              const int *Bir, const int *Bic, float *C, int m_hint,
+                              bidmat_stream_t stream) {
+    return dsmultT_impl<float>(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, m_hint, as_stream(stream));
+}
+
+int bidmat_b200_dds_async(int nrows, int nnz, const float *A, const float *B, const int *Cir,
+                          const int *Cic, float *P, bidmat_stream_t stream) {
+    return dds_impl<float>(nrows, nnz, A, B, Cir, Cic, P, as_stream(stream));
+}
+
+int bidmat_b200_dds0_async(int nrows, int ncols, int nnz, const float *A, const float *B,
+                           const int *Cir, const int *Cjc, float *P, bidmat_stream_t stream) {
+    return dds0_impl<float>(nrows, ncols, nnz, A, B, Cir, Cjc, P, as_stream(stream));
 }
 
 int bidmat_b200_transpose_csc(int nrows, int ncols, int nnz, const int *ir, const int *ic, const float *data,
@@ -439,7 +507,7 @@ int bidmat_b200_transpose_csc(int nrows, int ncols, int nnz, const int *ir, cons
     // key = old row (the new column); payload = (old column = new row, value).  The
     // sort is stable and ic is non-decreasing, so the new rows come out ascending
     // inside every new column, as a CSC matrix needs.
-    run_rowsort(nnz, passes, SortKeySpec{31, rowbits}, ir, ic, data, keys, cols, vals,
+    run_rowsort<float>(nnz, passes, SortKeySpec{31, rowbits}, ir, ic, data, keys, cols, vals,
                 reinterpret_cast<unsigned *>(t_ic), t_ir, t_data, counts, totals, st);
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return (int)err;
@@ -449,32 +517,6 @@ int bidmat_b200_transpose_csc(int nrows, int ncols, int nnz, const int *ir, cons
         err = cudaGetLastError();
     }
     return (int)err;
-}
-
-int bidmat_b200_dds_async(int nrows, int nnz, const float *A, const float *B, const int *Cir,
-                          const int *Cic, float *P, bidmat_stream_t stream) {
-    if (nrows < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
-    if (nnz == 0) return 0;
-    if (!A || !B || !Cir || !Cic || !P) return (int)cudaErrorInvalidValue;
-    if (nrows == 0) return 0;
-    return (int)launch_dds<true>(nrows, nnz, A, B, Cir, Cic, P, as_stream(stream));
-}
-
-int bidmat_b200_dds0_async(int nrows, int ncols, int nnz, const float *A, const float *B,
-                           const int *Cir, const int *Cjc, float *P, bidmat_stream_t stream) {
-    if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
-    if (nnz == 0 || ncols == 0) return 0;
-    if (!A || !B || !Cir || !Cjc || !P) return (int)cudaErrorInvalidValue;
-    cudaStream_t st = as_stream(stream);
-    if (nrows == 0) return (int)cudaMemsetAsync(P, 0, (size_t)nnz * sizeof(float), st);
-    WorkspaceLease ws(pad256((size_t)nnz * 4) + 256, st);
-    if (ws.err != cudaSuccess) return (int)ws.err;
-    int *ic = ws.take<int>((size_t)nnz);
-    expand_jc_kernel<<<(unsigned)(((size_t)nnz + kThreads - 1) / kThreads), kThreads, 0, st>>>(ncols, nnz, Cjc, ic);
-    g_launches += 1;
-    cudaError_t err = cudaGetLastError();
-    if (err != cudaSuccess) return (int)err;
-    return (int)launch_dds<false>(nrows, nnz, A, B, Cir, ic, P, st);
 }
 
 int bidmat_b200_dsmult(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
@@ -509,6 +551,56 @@ int bidmat_b200_dds0(int nrows, int ncols, const float *A, const float *B, const
     if (err == cudaSuccess) err = cudaStreamSynchronize(cudaStreamPerThread);
     if (err != cudaSuccess) return (int)err;
     int e = bidmat_b200_dds0_async(nrows, ncols, nnz, A, B, Cir, Cjc, P, cudaStreamPerThread);
+    return finish_sync((cudaError_t)e, cudaStreamPerThread);
+}
+
+// ---- double-precision twins (BIDMat's CUMATD natives)
+int bidmat_b200_dsmult_f64_async(int nrows, int ncols, int nnz, const double *A, const double *Bdata,
+                                 const int *Bir, const int *Bic, double *C, bidmat_stream_t stream) {
+    return dsmult_impl<double>(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, as_stream(stream));
+}
+
+int bidmat_b200_dsmultT_f64_async(int nrows, int ncols, int nnz, const double *A, const double *Bdata,
+                                  const int *Bir, const int *Bic, double *C, int m_hint, bidmat_stream_t stream) {
+    return dsmultT_impl<double>(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, m_hint, as_stream(stream));
+}
+
+int bidmat_b200_dds_f64_async(int nrows, int nnz, const double *A, const double *B, const int *Cir,
+                              const int *Cic, double *P, bidmat_stream_t stream) {
+    return dds_impl<double>(nrows, nnz, A, B, Cir, Cic, P, as_stream(stream));
+}
+
+int bidmat_b200_dsmult_f64(int nrows, int ncols, int nnz, const double *A, const double *Bdata,
+                           const int *Bir, const int *Bic, double *C) {
+    if (nrows >= 0 && ncols >= 0 && (nnz == 0 || nrows == 0)) return 0;
+    int e = dsmult_impl<double>(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, cudaStreamPerThread);
+    return finish_sync((cudaError_t)e, cudaStreamPerThread);
+}
+
+int bidmat_b200_dsmultT_f64(int nrows, int ncols, int nnz, const double *A, const double *Bdata,
+                            const int *Bir, const int *Bic, double *C) {
+    if (nrows >= 0 && ncols >= 0 && (nnz == 0 || nrows == 0)) return 0;
+    int e = dsmultT_impl<double>(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, 0, cudaStreamPerThread);
+    return finish_sync((cudaError_t)e, cudaStreamPerThread);
+}
+
+int bidmat_b200_dds_f64(int nrows, int nnz, const double *A, const double *B, const int *Cir,
+                        const int *Cic, double *P) {
+    if (nrows >= 0 && nnz == 0) return 0;
+    int e = dds_impl<double>(nrows, nnz, A, B, Cir, Cic, P, cudaStreamPerThread);
+    return finish_sync((cudaError_t)e, cudaStreamPerThread);
+}
+
+int bidmat_b200_dds0_f64(int nrows, int ncols, const double *A, const double *B, const int *Cir,
+                         const int *Cjc, double *P) {
+    if (nrows < 0 || ncols < 0) return (int)cudaErrorInvalidValue;
+    if (ncols == 0) return 0;
+    if (!Cjc) return (int)cudaErrorInvalidValue;
+    int nnz = 0;
+    cudaError_t err = cudaMemcpyAsync(&nnz, Cjc + ncols, sizeof(int), cudaMemcpyDeviceToHost, cudaStreamPerThread);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(cudaStreamPerThread);
+    if (err != cudaSuccess) return (int)err;
+    int e = dds0_impl<double>(nrows, ncols, nnz, A, B, Cir, Cjc, P, cudaStreamPerThread);
     return finish_sync((cudaError_t)e, cudaStreamPerThread);
 }
 
@@ -602,7 +694,7 @@ int bidmat_b200_spsum(int nrows, int ncols, int nnz, const int *Air, const int *
         if (err != cudaSuccess) return (int)err;
         fill_one_kernel<<<1, 1, 0, st>>>(one);
         g_launches += 1;
-        err = launch_ga(1, nnz, one, P, zeros, Aic, B, part, chunk, s, st, "spsum_ga_chunk");
+        err = launch_ga<float>(1, nnz, one, P, zeros, Aic, B, part, chunk, s, st, "spsum_ga_chunk");
         return finish_sync(err, st);
     }
     // B(nrows x 1)[ir[j]] += P[j]: stable sort by row first, then the same kernel
@@ -625,12 +717,12 @@ int bidmat_b200_spsum(int nrows, int ncols, int nnz, const int *Air, const int *
     if (err != cudaSuccess) return (int)err;
     fill_one_kernel<<<1, 1, 0, st>>>(one);
     g_launches += 1;
-    const int cur = run_rowsort(nnz, (rowbits + 7) / 8, SortKeySpec{31, rowbits}, Air, Aic, P, keys, cols, vals,
-                                nullptr, nullptr, nullptr, counts, totals, st);
+    const int cur = run_rowsort<float>(nnz, (rowbits + 7) / 8, SortKeySpec{31, rowbits}, Air, Aic, P, keys, cols, vals,
+                                       nullptr, nullptr, nullptr, counts, totals, st);
     err = cudaGetLastError();
     if (err != cudaSuccess) return (int)err;
-    err = launch_ga(1, nnz, one, vals[cur], zeros, reinterpret_cast<const int *>(keys[cur]), B, part, chunk, s, st,
-                    "spsum_ga_chunk");
+    err = launch_ga<float>(1, nnz, one, vals[cur], zeros, reinterpret_cast<const int *>(keys[cur]), B, part, chunk, s,
+                           st, "spsum_ga_chunk");
     return finish_sync(err, st);
 }
 

@@ -8,9 +8,11 @@ namespace bidmat {
 // A "worker" is a group of LPV consecutive lanes of one warp (LPV in
 // {8,16,32}).  Lane l of a worker owns the VEC-wide elements l, l+LPV,
 // l+2*LPV, ... (NT of them) of a dense column, so a worker reads a column
-// with fully coalesced 16-byte loads when VEC == 4.
-template <int VEC> struct Vec;
-template <> struct Vec<1> {
+// with fully coalesced 16-byte loads when VEC > 1.
+// Vec<S, VEC>: VEC scalars of type S moved as one load/store (16 bytes when
+// VEC > 1: float4 or double2).
+template <typename S, int VEC> struct Vec;
+template <> struct Vec<float, 1> {
     typedef float T;
     static __device__ __forceinline__ T zero() { return 0.f; }
     static __device__ __forceinline__ T ldg(const float *p) { return __ldg(p); }
@@ -20,7 +22,7 @@ template <> struct Vec<1> {
     static __device__ __forceinline__ void add(T &acc, const T &x) { acc += x; }
     static __device__ __forceinline__ float dot(const T &a, const T &b, float acc) { return fmaf(a, b, acc); }
 };
-template <> struct Vec<4> {
+template <> struct Vec<float, 4> {
     typedef float4 T;
     static __device__ __forceinline__ T zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
     static __device__ __forceinline__ T ldg(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
@@ -36,6 +38,31 @@ template <> struct Vec<4> {
     static __device__ __forceinline__ float dot(const T &a, const T &b, float acc) {
         acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc);
         acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+        return acc;
+    }
+};
+template <> struct Vec<double, 1> {
+    typedef double T;
+    static __device__ __forceinline__ T zero() { return 0.0; }
+    static __device__ __forceinline__ T ldg(const double *p) { return __ldg(p); }
+    static __device__ __forceinline__ T ld(const double *p) { return *p; }
+    static __device__ __forceinline__ void st(double *p, T v) { *p = v; }
+    static __device__ __forceinline__ void fma(T &acc, double s, const T &x) { acc = ::fma(s, x, acc); }
+    static __device__ __forceinline__ void add(T &acc, const T &x) { acc += x; }
+    static __device__ __forceinline__ double dot(const T &a, const T &b, double acc) { return ::fma(a, b, acc); }
+};
+template <> struct Vec<double, 2> {
+    typedef double2 T;
+    static __device__ __forceinline__ T zero() { return make_double2(0.0, 0.0); }
+    static __device__ __forceinline__ T ldg(const double *p) { return __ldg(reinterpret_cast<const double2 *>(p)); }
+    static __device__ __forceinline__ T ld(const double *p) { return *reinterpret_cast<const double2 *>(p); }
+    static __device__ __forceinline__ void st(double *p, T v) { *reinterpret_cast<double2 *>(p) = v; }
+    static __device__ __forceinline__ void fma(T &acc, double s, const T &x) {
+        acc.x = ::fma(s, x.x, acc.x); acc.y = ::fma(s, x.y, acc.y);
+    }
+    static __device__ __forceinline__ void add(T &acc, const T &x) { acc.x += x.x; acc.y += x.y; }
+    static __device__ __forceinline__ double dot(const T &a, const T &b, double acc) {
+        acc = ::fma(a.x, b.x, acc); acc = ::fma(a.y, b.y, acc);
         return acc;
     }
 };

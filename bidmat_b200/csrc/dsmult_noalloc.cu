@@ -88,12 +88,13 @@ extern "C" int bidmat_b200_dsmult_noalloc(int nrows, int ncols, int nnz, const f
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : cudaStreamPerThread;
     dim3 grid(blocks_for(nchunks, s.lpv), s.tiles, 1);
     const int ichunk = (int)chunk;
+    constexpr int kWideVec = 4;
 #define CALL_GA_NOALLOC(VEC, LPV, NT)                                                                  \
-    ga_chunk_kernel<VEC, LPV, NT, 4><<<grid, kThreads, 0, st>>>(nrows, nnz, ichunk, nchunks, A, Bdata, \
+    ga_chunk_kernel<float, VEC, LPV, NT, 4><<<grid, kThreads, 0, st>>>(nrows, nnz, ichunk, nchunks, A, Bdata, \
                                                                 Bir, Bic, C, part, nullptr,           \
                                                                 0xffffffffu);                          \
     if (nchunks > 1)                                                                                   \
-        ga_fixup_kernel<VEC, LPV, NT><<<grid, kThreads, 0, st>>>(nrows, nnz, ichunk, nchunks, Bic, C, part, nullptr, \
+        ga_fixup_kernel<float, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(nrows, nnz, ichunk, nchunks, Bic, C, part, nullptr, \
                                                                  0xffffffffu);
     DISPATCH_SHAPE(s, CALL_GA_NOALLOC);
 #undef CALL_GA_NOALLOC

@@ -15,15 +15,15 @@ inline std::atomic<long long> g_launches{0};
 
 // How a dense column of height k is spread over a worker.
 struct Shape {
-    int vec;   // 4 when k % 4 == 0 and the pointers are 16-byte aligned, else 1
+    int vec;   // 16-byte vectors (4 floats / 2 doubles) when k allows and the pointers are aligned, else 1
     int lpv;   // lanes per worker
     int nt;    // VEC-wide elements per lane
     int tiles; // k-tiles of width lpv*nt*vec
 };
 
-inline Shape pick_shape(int k, bool aligned16) {
+inline Shape pick_shape(int k, bool aligned16, int wide = 4) {
     Shape s;
-    s.vec = (aligned16 && (k % 4 == 0)) ? 4 : 1;
+    s.vec = (aligned16 && (k % wide == 0)) ? wide : 1;
     const int kv = k / s.vec;
     if (kv <= 8) { s.lpv = 8; s.nt = 1; }
     else if (kv <= 16) { s.lpv = 16; s.nt = 1; }
@@ -72,14 +72,15 @@ inline long long max_chunks_for(long long nnz, int lpv) {
     return alt > cap ? alt : cap;
 }
 
+// Expects `kWideVec` (4 for float, 2 for double) as a constant in the calling scope.
 #define DISPATCH_SHAPE(S, CALL)                                                     \
     do {                                                                            \
-        if ((S).vec == 4) {                                                         \
-            if ((S).lpv == 8) { CALL(4, 8, 1); }                                    \
-            else if ((S).lpv == 16) { CALL(4, 16, 1); }                             \
-            else if ((S).nt == 1) { CALL(4, 32, 1); }                               \
-            else if ((S).nt == 2) { CALL(4, 32, 2); }                               \
-            else { CALL(4, 32, 4); }                                                \
+        if ((S).vec > 1) {                                                          \
+            if ((S).lpv == 8) { CALL(kWideVec, 8, 1); }                             \
+            else if ((S).lpv == 16) { CALL(kWideVec, 16, 1); }                      \
+            else if ((S).nt == 1) { CALL(kWideVec, 32, 1); }                        \
+            else if ((S).nt == 2) { CALL(kWideVec, 32, 2); }                        \
+            else { CALL(kWideVec, 32, 4); }                                         \
         } else {                                                                    \
             if ((S).lpv == 8) { CALL(1, 8, 1); }                                    \
             else if ((S).lpv == 16) { CALL(1, 16, 1); }                             \

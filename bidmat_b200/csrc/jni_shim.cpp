@@ -115,6 +115,41 @@ JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_sdopcol(JNIEnv *env, jclass, 
                                (const int *)device_address(env, jAir), (const float *)device_address(env, jB), len, opn);
 }
 
+// Double-precision natives of edu.berkeley.bid.CUMATD (CUMATD.java:51,57,89,91).
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMATD_dsmult(JNIEnv *env, jclass, jint nrows, jint ncols, jint nnz,
+                                                          jobject jA, jobject jBdata, jobject jBir, jobject jBic,
+                                                          jobject jC) {
+    if (!init_field_ids(env)) return 1;
+    return bidmat_b200_dsmult_f64(nrows, ncols, nnz, (const double *)device_address(env, jA),
+                                  (const double *)device_address(env, jBdata), (const int *)device_address(env, jBir),
+                                  (const int *)device_address(env, jBic), (double *)device_address(env, jC));
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMATD_dsmultT(JNIEnv *env, jclass, jint nrows, jint ncols, jint nnz,
+                                                           jobject jA, jobject jBdata, jobject jBir, jobject jBic,
+                                                           jobject jC) {
+    if (!init_field_ids(env)) return 1;
+    return bidmat_b200_dsmultT_f64(nrows, ncols, nnz, (const double *)device_address(env, jA),
+                                   (const double *)device_address(env, jBdata), (const int *)device_address(env, jBir),
+                                   (const int *)device_address(env, jBic), (double *)device_address(env, jC));
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMATD_dds(JNIEnv *env, jclass, jint nrows, jint nnz, jobject jA,
+                                                       jobject jB, jobject jCir, jobject jCic, jobject jP) {
+    if (!init_field_ids(env)) return 1;
+    return bidmat_b200_dds_f64(nrows, nnz, (const double *)device_address(env, jA),
+                               (const double *)device_address(env, jB), (const int *)device_address(env, jCir),
+                               (const int *)device_address(env, jCic), (double *)device_address(env, jP));
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMATD_dds0(JNIEnv *env, jclass, jint nrows, jint ncols, jobject jA,
+                                                        jobject jB, jobject jCir, jobject jCjc, jobject jP) {
+    if (!init_field_ids(env)) return 1;
+    return bidmat_b200_dds0_f64(nrows, ncols, (const double *)device_address(env, jA),
+                                (const double *)device_address(env, jB), (const int *)device_address(env, jCir),
+                                (const int *)device_address(env, jCjc), (double *)device_address(env, jP));
+}
+
 // Route (ii): rebind the four natives when this library is loaded by System.load.
 JNIEXPORT jint JNICALL JNI_OnLoad(JavaVM *vm, void *) {
     JNIEnv *env = nullptr;

@@ -24,14 +24,14 @@ namespace bidmat {
 // Dense column layout per worker: lane l holds VEC-wide elements l + t*LPV,
 // t < NT, of the k-tile selected by blockIdx.y (tile width LPV*NT*VEC floats).
 // ---------------------------------------------------------------------------
-template <int VEC, int LPV, int NT, int U>
+template <typename S, int VEC, int LPV, int NT, int U>
 __global__ void __launch_bounds__(kThreads)
 ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
-                const float *__restrict__ D, const float *__restrict__ val,
+                const S *__restrict__ D, const S *__restrict__ val,
                 const int *__restrict__ gidx, const int *__restrict__ seg,
-                float *__restrict__ O, float *__restrict__ part,
+                S *__restrict__ O, S *__restrict__ part,
                 const int *__restrict__ range, unsigned segmask) {
-    typedef Vec<VEC> V;
+    typedef Vec<S, VEC> V;
     typedef typename V::T VT;
     const int lane = threadIdx.x & (LPV - 1);
     const unsigned mask = worker_mask<LPV>();
@@ -63,7 +63,7 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
 
     auto flush = [&](bool tail_open) {
         if (!head_open && !tail_open) {
-            float *o = O + (size_t)((unsigned)cur & segmask) * k;
+            S *o = O + (size_t)((unsigned)cur & segmask) * k;
 #pragma unroll
             for (int t = 0; t < NT; t++)
                 if (eok[t]) {
@@ -72,7 +72,7 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
                     V::st(o + eoff[t], old);
                 }
         } else {
-            float *p = part + ((size_t)c * 2 + (head_open ? 0 : 1)) * k;
+            S *p = part + ((size_t)c * 2 + (head_open ? 0 : 1)) * k;
 #pragma unroll
             for (int t = 0; t < NT; t++)
                 if (eok[t]) V::st(p + eoff[t], acc[t]);
@@ -83,20 +83,20 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
         long long jj = base + lane;
         if (jj >= j1) jj = j1 - 1;  // padded lanes repeat the last entry; never accumulated
         const int my_idx = __ldg(gidx + jj);
-        const float my_val = __ldg(val + jj);
+        const S my_val = __ldg(val + jj);
         const int my_seg = __ldg(seg + jj);
         const int cnt = (j1 - base < LPV) ? (int)(j1 - base) : LPV;
         for (int t0 = 0; t0 < cnt; t0 += U) {
             VT x[U][NT];
             int s[U];
-            float v[U];
+            S v[U];
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const int src = (t0 + u) & (LPV - 1);
                 const int i = __shfl_sync(mask, my_idx, src, LPV);
                 v[u] = __shfl_sync(mask, my_val, src, LPV);
                 s[u] = __shfl_sync(mask, my_seg, src, LPV);
-                const float *d = D + (size_t)i * k;
+                const S *d = D + (size_t)i * k;
 #pragma unroll
                 for (int t = 0; t < NT; t++) x[u][t] = eok[t] ? V::ldg(d + eoff[t]) : V::zero();
             }
@@ -125,12 +125,12 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
 // search: seg is non-decreasing as unsigned keys), adds the stored pieces in
 // chunk order, with the loads issued four chunks ahead of the adds, and adds the
 // total to O.  Every other worker returns.
-template <int VEC, int LPV, int NT>
+template <typename S, int VEC, int LPV, int NT>
 __global__ void __launch_bounds__(kThreads)
 ga_fixup_kernel(int k, long long nnz, int chunk, long long nchunks,
-                const int *__restrict__ seg, float *__restrict__ O,
-                const float *__restrict__ part, const int *__restrict__ range, unsigned segmask) {
-    typedef Vec<VEC> V;
+                const int *__restrict__ seg, S *__restrict__ O,
+                const S *__restrict__ part, const int *__restrict__ range, unsigned segmask) {
+    typedef Vec<S, VEC> V;
     typedef typename V::T VT;
     const int lane = threadIdx.x & (LPV - 1);
     const long long c = ((long long)blockIdx.x * kThreads + threadIdx.x) / LPV;
@@ -168,7 +168,7 @@ ga_fixup_kernel(int k, long long nnz, int chunk, long long nchunks,
 #pragma unroll
         for (int q = 0; q < PF; q++) {
             const long long dd = (d + q <= dend) ? d + q : dend;
-            const float *p = part + (size_t)dd * 2 * k;
+            const S *p = part + (size_t)dd * 2 * k;
 #pragma unroll
             for (int t = 0; t < NT; t++) x[q][t] = eok[t] ? V::ld(p + eoff[t]) : V::zero();
         }
@@ -179,7 +179,7 @@ ga_fixup_kernel(int k, long long nnz, int chunk, long long nchunks,
                 for (int t = 0; t < NT; t++) V::add(tot[t], x[q][t]);
             }
     }
-    float *o = O + (size_t)((unsigned)s & segmask) * k;
+    S *o = O + (size_t)((unsigned)s & segmask) * k;
 #pragma unroll
     for (int t = 0; t < NT; t++)
         if (eok[t]) {
@@ -490,12 +490,12 @@ dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
 // A k-tile wider than LPV*NT*VEC is handled by looping over tiles inside the
 // worker so that P is written once.
 // ---------------------------------------------------------------------------
-template <int VEC, int LPV, int NT, int U, bool ACCUM>
+template <typename S, int VEC, int LPV, int NT, int U, bool ACCUM>
 __global__ void __launch_bounds__(kThreads)
 dds_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
-                 const float *__restrict__ A, const float *__restrict__ B,
-                 const int *__restrict__ ir, const int *__restrict__ ic, float *__restrict__ P) {
-    typedef Vec<VEC> V;
+                 const S *__restrict__ A, const S *__restrict__ B,
+                 const int *__restrict__ ir, const int *__restrict__ ic, S *__restrict__ P) {
+    typedef Vec<S, VEC> V;
     typedef typename V::T VT;
     const int lane = threadIdx.x & (LPV - 1);
     const unsigned mask = worker_mask<LPV>();
@@ -519,7 +519,7 @@ dds_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
         const int my_ir = __ldg(ir + jj);
         const int my_ic = __ldg(ic + jj);
         const int cnt = (j1 - base < LPV) ? (int)(j1 - base) : LPV;
-        float mine = 0.f;
+        S mine = 0;
         for (int tile = 0; tile < ntiles; tile++) {
             int eoff[NT];
             bool eok[NT];
@@ -537,7 +537,7 @@ dds_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
                     const int src = (t0 + u) & (LPV - 1);
                     const int i = __shfl_sync(mask, my_ir, src, LPV);
                     cc[u] = __shfl_sync(mask, my_ic, src, LPV);
-                    const float *a = A + (size_t)i * k;
+                    const S *a = A + (size_t)i * k;
 #pragma unroll
                     for (int t = 0; t < NT; t++) x[u][t] = eok[t] ? V::ldg(a + eoff[t]) : V::zero();
                 }
@@ -546,11 +546,11 @@ dds_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
                     if (t0 + u < cnt) {
                         if (cc[u] != cur) {
                             cur = cc[u];
-                            const float *bp = B + (size_t)cur * k;
+                            const S *bp = B + (size_t)cur * k;
 #pragma unroll
                             for (int t = 0; t < NT; t++) b[t] = eok[t] ? V::ldg(bp + eoff[t]) : V::zero();
                         }
-                        float p = 0.f;
+                        S p = 0;
 #pragma unroll
                         for (int t = 0; t < NT; t++) p = V::dot(x[u][t], b[t], p);
 #pragma unroll

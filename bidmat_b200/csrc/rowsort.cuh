@@ -127,24 +127,24 @@ __global__ void __launch_bounds__(256) sort_digit_base_kernel(int *__restrict__ 
     for (int g = 0; g < kSortScanSegs; g++) seg_tot[d * kSortScanSegs + g] += base;
 }
 
-struct SortSmem {
+template <typename PV> struct SortSmem {
+    PV b[kSortTile];                   // value payload (float or double), first for alignment
     unsigned key[kSortTile];
     int a[kSortTile];
-    float b[kSortTile];
     int warp_count[kSortWarps][256];   // per-warp digit counts, then exclusive offsets over warps
     int digit_start[256];              // first slot of each digit in the sorted tile
     int global_base[256];              // first output slot of this tile's keys of each digit
     int scan_tmp[kSortWarps];
 };
 
-template <bool FIRST>
-__global__ void __launch_bounds__(kSortThreads, 3)
+template <bool FIRST, typename PV>
+__global__ void __launch_bounds__(kSortThreads, (sizeof(PV) == 4 ? 3 : 2))
 sort_scatter_kernel(long long n, int ntiles, int shift, SortKeySpec ks, const unsigned *__restrict__ keys_in,
-                    const int *__restrict__ ir, const int *__restrict__ a_in, const float *__restrict__ b_in,
+                    const int *__restrict__ ir, const int *__restrict__ a_in, const PV *__restrict__ b_in,
                     const int *__restrict__ counts, const int *__restrict__ seg_base, int tps,
-                    unsigned *__restrict__ keys_out, int *__restrict__ a_out, float *__restrict__ b_out) {
+                    unsigned *__restrict__ keys_out, int *__restrict__ a_out, PV *__restrict__ b_out) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    SortSmem &sm = *reinterpret_cast<SortSmem *>(smem_raw);
+    SortSmem<PV> &sm = *reinterpret_cast<SortSmem<PV> *>(smem_raw);
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const long long tile_base = (long long)blockIdx.x * kSortTile;
     const int tile_n = (int)((n - tile_base < kSortTile) ? (n - tile_base) : kSortTile);
@@ -158,7 +158,7 @@ sort_scatter_kernel(long long n, int ntiles, int shift, SortKeySpec ks, const un
     // consecutive positions, so (warp, round, lane) order is input order.
     unsigned key[kSortKeysPerThread];
     int pa[kSortKeysPerThread];
-    float pb[kSortKeysPerThread];
+    PV pb[kSortKeysPerThread];
     int rank[kSortKeysPerThread];
 #pragma unroll
     for (int r = 0; r < kSortKeysPerThread; r++) {
@@ -166,7 +166,7 @@ sort_scatter_kernel(long long n, int ntiles, int shift, SortKeySpec ks, const un
         const bool ok = pos < tile_n;
         key[r] = 0;
         pa[r] = 0;
-        pb[r] = 0.f;
+        pb[r] = 0;
         if (ok) {
             const long long j = tile_base + pos;
             pa[r] = __ldg(a_in + j);

@@ -102,6 +102,28 @@ BIDMAT_B200_API int bidmat_b200_dds_async(int nrows, int nnz, const float *A, co
 BIDMAT_B200_API int bidmat_b200_dds0_async(int nrows, int ncols, int nnz, const float *A, const float *B,
                            const int *Cir, const int *Cjc, float *P, bidmat_stream_t stream);
 
+/* Double-precision twins of the four operations (BIDMat's GDMat / GSDMat path).
+ * Same semantics as the fp32 functions above; dense operands and values are fp64.
+ * Replaces: dsmult / dsmultT / dds / dds0 on doubles (jni/include/MatKernelD.hpp:43,49,53,55,
+ *   jni/src/MatKernelD.cu:780-1030, CUMATD.java:51,57,89,91). */
+BIDMAT_B200_API int bidmat_b200_dsmult_f64(int nrows, int ncols, int nnz, const double *A, const double *Bdata,
+                                           const int *Bir, const int *Bic, double *C);
+BIDMAT_B200_API int bidmat_b200_dsmultT_f64(int nrows, int ncols, int nnz, const double *A, const double *Bdata,
+                                            const int *Bir, const int *Bic, double *C);
+BIDMAT_B200_API int bidmat_b200_dds_f64(int nrows, int nnz, const double *A, const double *B, const int *Cir,
+                                        const int *Cic, double *P);
+BIDMAT_B200_API int bidmat_b200_dds0_f64(int nrows, int ncols, const double *A, const double *B, const int *Cir,
+                                         const int *Cjc, double *P);
+BIDMAT_B200_API int bidmat_b200_dsmult_f64_async(int nrows, int ncols, int nnz, const double *A,
+                                                 const double *Bdata, const int *Bir, const int *Bic,
+                                                 double *C, bidmat_stream_t stream);
+BIDMAT_B200_API int bidmat_b200_dsmultT_f64_async(int nrows, int ncols, int nnz, const double *A,
+                                                  const double *Bdata, const int *Bir, const int *Bic,
+                                                  double *C, int m_hint, bidmat_stream_t stream);
+BIDMAT_B200_API int bidmat_b200_dds_f64_async(int nrows, int nnz, const double *A, const double *B,
+                                              const int *Cir, const int *Cic, double *P,
+                                              bidmat_stream_t stream);
+
 /* A*S without any allocation.  No counterpart in the reference: BIDMat's
  * launchers never needed scratch memory.  It exists for callers that cannot let a
  * library allocate on the device: host applications that have handed all device

@@ -5,4 +5,5 @@ from .cpu_oracle import (  # noqa: F401
     dsmult, dsmultT, dds, dsmult_f64, dsmultT_f64, dds_f64,
     uncompress_inds, compress_inds, check_csc,
     ref_available, ref_smcscm, ref_smcsrm,
+    dsmult_d, dsmultT_d, dds_d, ref_dmcscm, ref_dmcsrm,
 )

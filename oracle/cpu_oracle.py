@@ -44,6 +44,12 @@ def _load():
         _lib.oracle_dds_f64.argtypes = [ctypes.c_int, ctypes.c_int, _F32P, _F32P, _I32P, _I32P,
                                         _F64P, _F64P, ctypes.c_int]
         _lib.oracle_dds_f64.restype = None
+        for name in ("oracle_dsmultT_d", "oracle_dds_d"):
+            getattr(_lib, name).restype = None
+        _lib.oracle_dsmult_d.argtypes = [ctypes.c_int, ctypes.c_int, _F64P, _F64P, _I32P, _I32P, _F64P, ctypes.c_int]
+        _lib.oracle_dsmult_d.restype = None
+        _lib.oracle_dsmultT_d.argtypes = [ctypes.c_int, ctypes.c_int, _F64P, _F64P, _I32P, _I32P, _F64P]
+        _lib.oracle_dds_d.argtypes = [ctypes.c_int, ctypes.c_int, _F64P, _F64P, _I32P, _I32P, _F64P]
         _lib.oracle_uncompress_inds.argtypes = [_I32P, ctypes.c_int, _I32P]
         _lib.oracle_uncompress_inds.restype = None
         _lib.oracle_compress_inds.argtypes = [_I32P, ctypes.c_int, ctypes.c_int32, _I32P]
@@ -63,6 +69,10 @@ def _load_ref():
             for name in ("ref_smcscm", "ref_smcsrm"):
                 getattr(_ref, name).argtypes = [ctypes.c_int, ctypes.c_int, _F32P, _F32P, _I32P,
                                                 _I32P, _F32P]
+                getattr(_ref, name).restype = None
+            for name in ("ref_dmcscm", "ref_dmcsrm"):
+                getattr(_ref, name).argtypes = [ctypes.c_int, ctypes.c_int, _F64P, _F64P, _I32P,
+                                                _I32P, _F64P]
                 getattr(_ref, name).restype = None
     return _ref
 
@@ -238,4 +248,60 @@ def ref_smcsrm(B, data, ir, jc, m, out=None):
     if out is None:
         out = np.zeros((m, k), dtype=np.float32)
     lib.ref_smcsrm(k, n, pB, pd, pir, pjc, out.ctypes.data_as(_F32P))
+    return out
+
+
+# ---- double-precision operands (BIDMat's DMat / SDMat path)
+def _f64(a):
+    a = np.ascontiguousarray(a, dtype=np.float64)
+    return a, a.ctypes.data_as(_F64P)
+
+
+def dsmult_d(A, data, ir, jc, out=None, nthreads=None):
+    A, pA = _f64(A); k = _dense_k(A); data, pd = _f64(data); ir, pir = _i32(ir); jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    if out is None:
+        out = np.zeros((n, k), dtype=np.float64)
+    _load().oracle_dsmult_d(k, n, pA, pd, pir, pjc, out.ctypes.data_as(_F64P), nthreads or default_threads())
+    return out
+
+
+def dsmultT_d(B, data, ir, jc, m, out=None):
+    B, pB = _f64(B); k = _dense_k(B); data, pd = _f64(data); ir, pir = _i32(ir); jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    if out is None:
+        out = np.zeros((m, k), dtype=np.float64)
+    _load().oracle_dsmultT_d(k, n, pB, pd, pir, pjc, out.ctypes.data_as(_F64P))
+    return out
+
+
+def dds_d(A, B, ir, jc):
+    A, pA = _f64(A); B, pB = _f64(B); k = _dense_k(A); ir, pir = _i32(ir); jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    out = np.zeros(len(ir), dtype=np.float64)
+    _load().oracle_dds_d(k, n, pA, pB, pir, pjc, out.ctypes.data_as(_F64P))
+    return out
+
+
+def ref_dmcscm(A, data, ir, jc, out=None):
+    lib = _load_ref()
+    if lib is None:
+        raise RuntimeError("reference build oracle/_ref/libspblas_ref.so is not available")
+    A, pA = _f64(A); k = _dense_k(A); data, pd = _f64(data); ir, pir = _i32(ir); jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    if out is None:
+        out = np.zeros((n, k), dtype=np.float64)
+    lib.ref_dmcscm(k, n, pA, pd, pir, pjc, out.ctypes.data_as(_F64P))
+    return out
+
+
+def ref_dmcsrm(B, data, ir, jc, m, out=None):
+    lib = _load_ref()
+    if lib is None:
+        raise RuntimeError("reference build oracle/_ref/libspblas_ref.so is not available")
+    B, pB = _f64(B); k = _dense_k(B); data, pd = _f64(data); ir, pir = _i32(ir); jc, pjc = _i32(jc)
+    n = len(jc) - 1
+    if out is None:
+        out = np.zeros((m, k), dtype=np.float64)
+    lib.ref_dmcsrm(k, n, pB, pd, pir, pjc, out.ctypes.data_as(_F64P))
     return out

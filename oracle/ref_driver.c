@@ -49,3 +49,21 @@ void ref_smcsrm(int k, int n, float *B, float *data, int *ir, int *jc, float *C)
     JNIEnv env = &table;
     Java_edu_berkeley_bid_SPBLAS_smcsrm(&env, NULL, k, n, B, k, data, ir, jc, C, k);
 }
+
+JNIEXPORT void JNICALL Java_edu_berkeley_bid_SPBLAS_dmcscm(JNIEnv *, jobject, jint, jint, jdoubleArray,
+                                                          jint, jdoubleArray, jintArray, jintArray,
+                                                          jdoubleArray, jint);
+JNIEXPORT void JNICALL Java_edu_berkeley_bid_SPBLAS_dmcsrm(JNIEnv *, jobject, jint, jint, jdoubleArray,
+                                                          jint, jdoubleArray, jintArray, jintArray,
+                                                          jdoubleArray, jint);
+
+/* Double-precision twins: dmcscm / dmcsrm (BIDMat_SPBLAS.c:294-360). */
+void ref_dmcscm(int k, int n, double *A, double *data, int *ir, int *jc, double *C) {
+    JNIEnv env = &table;
+    Java_edu_berkeley_bid_SPBLAS_dmcscm(&env, NULL, k, n, A, k, data, ir, jc, C, k);
+}
+
+void ref_dmcsrm(int k, int n, double *B, double *data, int *ir, int *jc, double *C) {
+    JNIEnv env = &table;
+    Java_edu_berkeley_bid_SPBLAS_dmcsrm(&env, NULL, k, n, B, k, data, ir, jc, C, k);
+}

@@ -212,3 +212,59 @@ int oracle_check_csc(int m, int n, int32_t nnz, const int32_t *ir, const int32_t
     if (jc[n] != nnz) return 6;
     return 0;
 }
+
+/* Double-precision inputs and outputs: the same three loops on doubles, the CPU
+ * counterpart of BIDMat's GDMat / GSDMat path.  A*S and B*^S are pinned
+ * bit-exactly to the reference's own dmcscm / dmcsrm
+ * (jni/src/BIDMat_SPBLAS.c:294-360); DDS on doubles is unpinned like its fp32 twin. */
+void oracle_dsmult_d(int k, int n, const double *A, const double *data, const int32_t *ir,
+                     const int32_t *jc, double *C, int nthreads) {
+    if (nthreads < 1) nthreads = 1;
+#pragma omp parallel for num_threads(nthreads) schedule(static, 1)
+    for (int t = 0; t < nthreads; t++) {
+        int istart = (int)((int64_t)t * n / nthreads);
+        int iend = (int)((int64_t)(t + 1) * n / nthreads);
+        for (int i = istart; i < iend; i++) {
+            double *out = C + (size_t)i * k;
+            for (int j = jc[i]; j < jc[i + 1]; j++) {
+                double dval = data[j];
+                const double *a = A + (size_t)ir[j] * k;
+                for (int kk = 0; kk < k; kk++) {
+                    double prod = a[kk] * dval;
+                    out[kk] = out[kk] + prod;
+                }
+            }
+        }
+    }
+}
+
+void oracle_dsmultT_d(int k, int n, const double *B, const double *data, const int32_t *ir,
+                      const int32_t *jc, double *C) {
+    for (int i = 0; i < n; i++) {
+        const double *b = B + (size_t)i * k;
+        for (int j = jc[i]; j < jc[i + 1]; j++) {
+            double dval = data[j];
+            double *out = C + (size_t)ir[j] * k;
+            for (int kk = 0; kk < k; kk++) {
+                double prod = b[kk] * dval;
+                out[kk] = out[kk] + prod;
+            }
+        }
+    }
+}
+
+void oracle_dds_d(int k, int n, const double *A, const double *B, const int32_t *ir,
+                  const int32_t *jc, double *P) {
+    for (int i = 0; i < n; i++) {
+        const double *b = B + (size_t)i * k;
+        for (int j = jc[i]; j < jc[i + 1]; j++) {
+            const double *a = A + (size_t)ir[j] * k;
+            double dsum = 0.0;
+            for (int kk = 0; kk < k; kk++) {
+                double prod = a[kk] * b[kk];
+                dsum = dsum + prod;
+            }
+            P[j] = dsum;
+        }
+    }
+}

@@ -126,3 +126,22 @@ def test_empty_matrix_is_noop():
     assert not oracle.dsmult(A, e_f, e_i, jc).any()
     assert not oracle.dsmultT(B, e_f, e_i, jc, m).any()
     assert oracle.dds(A, B, e_i, jc).shape == (0,)
+
+
+@pytest.mark.skipif(not oracle.ref_available(), reason="reference build not present")
+@pytest.mark.parametrize("k,m,n,dens", [(64, 120, 90, 0.1), (5, 40, 33, 0.3)])
+def test_double_precision_oracle_matches_live_reference_build(k, m, n, dens):
+    """dmcscm / dmcsrm (BIDMat_SPBLAS.c:294-360), bit for bit."""
+    rng = np.random.default_rng(k + n)
+    jc, ir, data = random_csc(m, n, dens, rng, empty_cols=(2,))
+    data = data.astype(np.float64) * (1 + 1e-9)
+    A = rng.standard_normal((m, k))
+    B = rng.standard_normal((n, k))
+    C0 = rng.standard_normal((n, k))
+    G0 = rng.standard_normal((m, k))
+    assert np.array_equal(oracle.dsmult_d(A, data, ir, jc, out=C0.copy(), nthreads=3),
+                          oracle.ref_dmcscm(A, data, ir, jc, out=C0.copy()))
+    assert np.array_equal(oracle.dsmultT_d(B, data, ir, jc, m, out=G0.copy()),
+                          oracle.ref_dmcsrm(B, data, ir, jc, m, out=G0.copy()))
+    ic = oracle.uncompress_inds(jc)
+    assert np.allclose(oracle.dds_d(A, B, ir, jc), np.einsum("ij,ij->i", A[ir], B[ic]), rtol=1e-13, atol=1e-13)
