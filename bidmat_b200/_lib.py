@@ -37,6 +37,8 @@ _SIGNATURES = {
     "bidmat_b200_expand_jc": (_c_int, [_c_int, _c_int, _vp, _vp, _vp]),
     "bidmat_b200_compress_ic": (_c_int, [_c_int, _c_int, _vp, _vp, _vp]),
     "bidmat_b200_transpose_csc": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "bidmat_b200_dsmultTile": (_c_int, [_c_int, _c_int, _c_int, _c_int, _vp, _c_int, _vp, _vp, _vp, _c_int, _c_int,
+                                        _vp, _c_int, _c_int]),
     "bidmat_b200_sdoprow": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _c_int, _c_int]),
     "bidmat_b200_sdopcol": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _c_int, _c_int]),
     "bidmat_b200_spsum": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _c_int]),

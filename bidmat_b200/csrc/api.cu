@@ -17,6 +17,7 @@
 #include "structure_kernels.cuh"
 #include "rowsort.cuh"
 #include "edgeops.cuh"
+#include "tile_compact.cuh"
 #include "host_common.cuh"
 
 using namespace bidmat;
@@ -127,15 +128,17 @@ template <typename S>
 cudaError_t launch_ga(int k, long long nnz, const S *D, const S *val, const int *gidx,
                       const int *seg, S *O, S *part, int chunk, const Shape &s,
                       cudaStream_t st, const char *label, long long count = -1,
-                      const int *range = nullptr, unsigned segmask = 0xffffffffu) {
+                      const int *range = nullptr, unsigned segmask = 0xffffffffu, int ld_d = 0, int ld_o = 0) {
     constexpr int kWideVec = 16 / (int)sizeof(S);
+    if (ld_d <= 0) ld_d = k;     // leading dimensions: k unless the operands are tiles of larger matrices
+    if (ld_o <= 0) ld_o = k;
     if (count < 0) count = nnz;
     if (count == 0) return cudaSuccess;
     const long long nchunks = (count + chunk - 1) / chunk;
     dim3 grid(blocks_for(nchunks, s.lpv), s.tiles, 1);
     bool done = false;
     if constexpr (std::is_same<S, float>::value) {
-        if (fast_shape(k, s) && !env_int("BIDMAT_B200_GENERIC", 0)) {
+        if (fast_shape(k, s) && ld_d == k && ld_o == k && !env_int("BIDMAT_B200_GENERIC", 0)) {
             const int wpb = kFastThreads / s.lpv;
             dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
             ScopedSpan sp(label, st);
@@ -160,7 +163,7 @@ cudaError_t launch_ga(int k, long long nnz, const S *D, const S *val, const int 
         ScopedSpan sp(label, st);                                                               \
         ga_chunk_kernel<S, VEC, LPV, NT, 4><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, D, val, \
                                                                        gidx, seg, O, part, range, \
-                                                                       segmask);                \
+                                                                       segmask, ld_d, ld_o);    \
     }
         DISPATCH_SHAPE(s, CALL_GA);
 #undef CALL_GA
@@ -168,7 +171,7 @@ cudaError_t launch_ga(int k, long long nnz, const S *D, const S *val, const int 
     if (nchunks > 1) {
         ScopedSpan sp("ga_fixup", st);
 #define CALL_FIX(VEC, LPV, NT) \
-    ga_fixup_kernel<S, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, seg, O, part, range, segmask);
+    ga_fixup_kernel<S, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, seg, O, part, range, segmask, ld_o);
         DISPATCH_SHAPE(s, CALL_FIX);
 #undef CALL_FIX
     }
@@ -723,6 +726,66 @@ int bidmat_b200_spsum(int nrows, int ncols, int nnz, const int *Air, const int *
     if (err != cudaSuccess) return (int)err;
     err = launch_ga<float>(1, nnz, one, vals[cur], zeros, reinterpret_cast<const int *>(keys[cur]), B, part, chunk, s,
                            st, "spsum_ga_chunk");
+    return finish_sync(err, st);
+}
+
+// C(nr x nc tile) += A(nr x kk tile) * S[broff:broff+kk, bcoff:bcoff+nc]       (transpose == 0)
+// C(nr x nc tile) += A(nr x kk tile) * S[broff:broff+nc, bcoff:bcoff+kk]^T     (transpose != 0)
+int bidmat_b200_dsmultTile(int nr, int nc, int kk, int nnz, const float *A, int lda, const float *Bdata,
+                           const int *Bir, const int *Bic, int broff, int bcoff, float *C, int ldc, int transpose) {
+    if (nr < 0 || nc < 0 || kk < 0 || nnz < 0 || lda < nr || ldc < nr) return (int)cudaErrorInvalidValue;
+    if (nnz == 0 || nr == 0 || nc == 0 || kk == 0) return 0;
+    if (!A || !Bdata || !Bir || !Bic || !C) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = cudaStreamPerThread;
+    const size_t n_ = (size_t)nnz;
+    const int ctiles = (int)((n_ + kCompactTile - 1) / kCompactTile);
+    // rows and columns of S that the tile keeps
+    const int nrt = transpose ? nc : kk, nct = transpose ? kk : nc;
+    const bool aligned = is16(A) && is16(C) && (lda % 4 == 0) && (ldc % 4 == 0);
+    const Shape s = pick_shape(nr, aligned);
+    const int chunk_all = pick_chunk(nnz, s.lpv);
+    const size_t part_floats = (size_t)max_chunks_for(nnz, s.lpv) * 2 * (size_t)nr;
+    const int stiles = (int)((n_ + kSortTile - 1) / kSortTile);
+    size_t need = 3 * pad256(n_ * 4) + pad256(((size_t)ctiles + 1) * 4) + pad256(part_floats * 4) + 4096;
+    if (transpose) need += 6 * pad256(n_ * 4) + pad256((size_t)256 * stiles * 4) + pad256(256 * kSortScanSegs * 4);
+    WorkspaceLease ws(need, st);
+    if (ws.err != cudaSuccess) return (int)ws.err;
+    int *trow = ws.take<int>(n_);
+    int *tcol = ws.take<int>(n_);
+    float *tval = ws.take<float>(n_);
+    int *offs = ws.take<int>((size_t)ctiles + 1);
+    float *part = ws.take<float>(part_floats);
+
+    compact_count_kernel<<<ctiles, kCompactThreads, 0, st>>>(nnz, Bir, Bic, broff, nrt, bcoff, nct, offs);
+    compact_scan_kernel<<<1, 1024, 0, st>>>(ctiles, offs);
+    compact_scatter_kernel<float><<<ctiles, kCompactThreads, 0, st>>>(nnz, Bir, Bic, Bdata, broff, nrt, bcoff, nct, offs,
+                                                                      trow, tcol, tval);
+    g_launches += 3;
+    int kept = 0;
+    cudaError_t err = cudaMemcpyAsync(&kept, offs + ctiles, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+    if (err != cudaSuccess) return (int)err;
+    if (kept == 0) return (int)cudaGetLastError();
+    const int chunk = pick_chunk(kept, s.lpv);
+    if (!transpose) {
+        // tile-relative columns are still non-decreasing: gather-accumulate directly
+        err = launch_ga<float>(nr, kept, A, tval, trow, tcol, C, part, chunk, s, st, "tile_ga_chunk", -1, nullptr,
+                               0xffffffffu, lda, ldc);
+        return finish_sync(err, st);
+    }
+    // transposed tile: order the kept nonzeros by tile-relative row, then gather columns of A
+    unsigned *keys[2] = {ws.take<unsigned>((size_t)kept), ws.take<unsigned>((size_t)kept)};
+    int *cols[2] = {ws.take<int>((size_t)kept), ws.take<int>((size_t)kept)};
+    float *vals[2] = {ws.take<float>((size_t)kept), ws.take<float>((size_t)kept)};
+    int *counts = ws.take<int>((size_t)256 * stiles);
+    int *totals = ws.take<int>(256 * kSortScanSegs);
+    int rowbits = ceil_log2((unsigned long long)(nrt > 1 ? nrt : 2));
+    const int cur = run_rowsort<float>(kept, (rowbits + 7) / 8, SortKeySpec{31, rowbits}, trow, tcol, tval, keys, cols,
+                                       vals, nullptr, nullptr, nullptr, counts, totals, st);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return (int)err;
+    err = launch_ga<float>(nr, kept, A, vals[cur], cols[cur], reinterpret_cast<const int *>(keys[cur]), C, part, chunk, s,
+                           st, "tile_ga_chunk", -1, nullptr, 0xffffffffu, lda, ldc);
     return finish_sync(err, st);
 }
 

@@ -92,10 +92,10 @@ extern "C" int bidmat_b200_dsmult_noalloc(int nrows, int ncols, int nnz, const f
 #define CALL_GA_NOALLOC(VEC, LPV, NT)                                                                  \
     ga_chunk_kernel<float, VEC, LPV, NT, 4><<<grid, kThreads, 0, st>>>(nrows, nnz, ichunk, nchunks, A, Bdata, \
                                                                 Bir, Bic, C, part, nullptr,           \
-                                                                0xffffffffu);                          \
+                                                                0xffffffffu, nrows, nrows);            \
     if (nchunks > 1)                                                                                   \
         ga_fixup_kernel<float, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(nrows, nnz, ichunk, nchunks, Bic, C, part, nullptr, \
-                                                                 0xffffffffu);
+                                                                        0xffffffffu, nrows);
     DISPATCH_SHAPE(s, CALL_GA_NOALLOC);
 #undef CALL_GA_NOALLOC
     g_launches += (nchunks > 1) ? 2 : 1;

@@ -91,6 +91,17 @@ JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_dsmultxtune(JNIEnv *env, jcla
     return Java_edu_berkeley_bid_CUMAT_dsmult(env, c, nrows, ncols, nnz, jA, jBdata, jBir, jBic, jC);
 }
 
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_dsmultTile(JNIEnv *env, jclass, jint nr, jint nc, jint kk, jint nnz,
+                                                             jobject jA, jint lda, jobject jBdata, jobject jBir,
+                                                             jobject jBic, jint broff, jint bcoff, jobject jC, jint ldc,
+                                                             jint transpose) {
+    if (!init_field_ids(env)) return 1;
+    return bidmat_b200_dsmultTile(nr, nc, kk, nnz, (const float *)device_address(env, jA), lda,
+                                  (const float *)device_address(env, jBdata), (const int *)device_address(env, jBir),
+                                  (const int *)device_address(env, jBic), broff, bcoff,
+                                  (float *)device_address(env, jC), ldc, transpose);
+}
+
 JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_spsum(JNIEnv *env, jclass, jint nrows, jint ncols, jint nnz,
                                                         jobject jAir, jobject jAic, jobject jP, jobject jB, jint n) {
     if (!init_field_ids(env)) return 1;

@@ -30,7 +30,9 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
                 const S *__restrict__ D, const S *__restrict__ val,
                 const int *__restrict__ gidx, const int *__restrict__ seg,
                 S *__restrict__ O, S *__restrict__ part,
-                const int *__restrict__ range, unsigned segmask) {
+                const int *__restrict__ range, unsigned segmask, int ld_d, int ld_o) {
+    // ld_d / ld_o: distance in elements between consecutive columns of D and O
+    // (k for whole matrices, larger for tiles of bigger matrices)
     typedef Vec<S, VEC> V;
     typedef typename V::T VT;
     const int lane = threadIdx.x & (LPV - 1);
@@ -63,7 +65,7 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
 
     auto flush = [&](bool tail_open) {
         if (!head_open && !tail_open) {
-            S *o = O + (size_t)((unsigned)cur & segmask) * k;
+            S *o = O + (size_t)((unsigned)cur & segmask) * ld_o;
 #pragma unroll
             for (int t = 0; t < NT; t++)
                 if (eok[t]) {
@@ -96,7 +98,7 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
                 const int i = __shfl_sync(mask, my_idx, src, LPV);
                 v[u] = __shfl_sync(mask, my_val, src, LPV);
                 s[u] = __shfl_sync(mask, my_seg, src, LPV);
-                const S *d = D + (size_t)i * k;
+                const S *d = D + (size_t)i * ld_d;
 #pragma unroll
                 for (int t = 0; t < NT; t++) x[u][t] = eok[t] ? V::ldg(d + eoff[t]) : V::zero();
             }
@@ -129,7 +131,7 @@ template <typename S, int VEC, int LPV, int NT>
 __global__ void __launch_bounds__(kThreads)
 ga_fixup_kernel(int k, long long nnz, int chunk, long long nchunks,
                 const int *__restrict__ seg, S *__restrict__ O,
-                const S *__restrict__ part, const int *__restrict__ range, unsigned segmask) {
+                const S *__restrict__ part, const int *__restrict__ range, unsigned segmask, int ld_o) {
     typedef Vec<S, VEC> V;
     typedef typename V::T VT;
     const int lane = threadIdx.x & (LPV - 1);
@@ -179,7 +181,7 @@ ga_fixup_kernel(int k, long long nnz, int chunk, long long nchunks,
                 for (int t = 0; t < NT; t++) V::add(tot[t], x[q][t]);
             }
     }
-    S *o = O + (size_t)((unsigned)s & segmask) * k;
+    S *o = O + (size_t)((unsigned)s & segmask) * ld_o;
 #pragma unroll
     for (int t = 0; t < NT; t++)
         if (eok[t]) {

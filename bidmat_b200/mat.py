@@ -174,6 +174,32 @@ class GMat:
         _check(err, "GMult: CUDA kernel error in CUMAT.dsmultT")
         return out
 
+    # ---- tiles (GMat.scala:961-997) --------------------------------------
+    def _tile(self, nr, nc, kk, aroff, acoff, b, broff, bcoff, c, croff, ccoff, transpose, name):
+        b = GSMat.of(b, self.t.device)
+        if min(aroff, acoff, broff, bcoff, croff, ccoff, nr, nc, kk) < 0:
+            raise RuntimeError("%s: cant have negative offsets or dimensions" % name)
+        brows, bcols = (nc, kk) if transpose else (kk, nc)
+        if (aroff + nr > self.nrows or acoff + kk > self.ncols or broff + brows > b.nrows or bcoff + bcols > b.ncols
+                or croff + nr > c.nrows or ccoff + nc > c.ncols):
+            raise RuntimeError("%s: tile strays outside matrix dimensions" % name)
+        Mat.nflops += 2 * nr * b.nnz
+        err = _L.bidmat_b200_dsmultTile(nr, nc, kk, b.nnz, self.pdata + 4 * (aroff + acoff * self.nrows), self.nrows,
+                                        _ptr(b.pdata), _ptr(b.pir), _ptr(b.pic), broff, bcoff,
+                                        c.pdata + 4 * (croff + ccoff * c.nrows), c.nrows, 1 if transpose else 0)
+        _check(err, "CUMAT.%s error" % name)
+        return c
+
+    def tileMult(self, nr, nc, kk, aroff, acoff, b, broff, bcoff, c, croff, ccoff):
+        """c[croff:+nr, ccoff:+nc] += this[aroff:+nr, acoff:+kk] * b[broff:+kk, bcoff:+nc]
+        (GMat.tileMult with a GSMat operand, GMat.scala:961-979)."""
+        return self._tile(nr, nc, kk, aroff, acoff, b, broff, bcoff, c, croff, ccoff, False, "tileMult")
+
+    def tileMultNT(self, nr, nc, kk, aroff, acoff, b, broff, bcoff, c, croff, ccoff):
+        """c[croff:+nr, ccoff:+nc] += this[aroff:+nr, acoff:+kk] * b[broff:+nc, bcoff:+kk]^T
+        (GMat.tileMultNT, GMat.scala:981-997)."""
+        return self._tile(nr, nc, kk, aroff, acoff, b, broff, bcoff, c, croff, ccoff, True, "tileMultNT")
+
     # ---- operators (GMat.scala:1684-1686, 1746-1748, 1972-1976) ----------
     def __mul__(self, a):
         """`A * S`."""

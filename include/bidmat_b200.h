@@ -172,6 +172,21 @@ BIDMAT_B200_API int bidmat_b200_transpose_csc(int nrows, int ncols, int nnz, con
                                               const float *data, int *t_ir, int *t_ic, int *t_jc,
                                               float *t_data, bidmat_stream_t stream);
 
+/* Tiled products for BIDMat's TMat.  A is an nr x kk tile (leading dimension lda) of a
+ * dense matrix and C an nr x nc tile (leading dimension ldc); only the nonzeros of S
+ * inside the tile take part, with indices taken relative to (broff, bcoff):
+ *   transpose == 0: rows [broff, broff+kk), columns [bcoff, bcoff+nc):
+ *                   C[:, col-bcoff] += A[:, row-broff] * value
+ *   transpose != 0: rows [broff, broff+nc), columns [bcoff, bcoff+kk):
+ *                   C[:, row-broff] += A[:, col-bcoff] * value
+ * Accumulates without float atomics.  Synchronous.
+ * Replaces: dsmultTile / dsmultTileT (jni/include/MatKernel.hpp:142-144,
+ *   jni/src/Arith.cu:63-189, CUMAT.dsmultTile CUMAT.java:145-146,
+ *   Java_edu_berkeley_bid_CUMAT_dsmultTile BIDMat_CUMAT.cpp:1456-1471). */
+BIDMAT_B200_API int bidmat_b200_dsmultTile(int nr, int nc, int kk, int nnz, const float *A, int lda,
+                                           const float *Bdata, const int *Bir, const int *Bic, int broff,
+                                           int bcoff, float *C, int ldc, int transpose);
+
 /* Edge operators on the values of a GSMat: A[j] = op(A[j], B[Aic[j]]) (sdoprow, B is
  * a 1 x ncols row) or op(A[j], B[Air[j]]) (sdopcol, B is an nrows x 1 column); with
  * len == 1 every value is combined with B[0].  opn indexes BIDMat's operator table

@@ -88,3 +88,42 @@ def test_mirror_sum_and_edge_operators(cuda_device):
     assert np.array_equal(aa.pdata.cpu().numpy(), data)       # operands are not modified
     with pytest.raises(RuntimeError, match="only edge operators"):
         aa + GMat.zeros(m, n, cuda_device)
+
+
+@pytest.mark.parametrize("nr,nc,kk,offs", [(8, 20, 30, (0, 0, 0, 0, 0, 0)), (12, 17, 23, (3, 5, 7, 11, 2, 4)),
+                                           (128, 40, 64, (0, 16, 32, 8, 0, 8)), (130, 33, 50, (1, 2, 3, 4, 5, 6))])
+def test_tile_products_against_dense(cuda_device, nr, nc, kk, offs, monkeypatch):
+    """GMat.tileMult / tileMultNT with a sparse operand (dsmultTile, dsmultTileT):
+    only the nonzeros inside the tile count, everything outside the output tile
+    stays untouched, and the product accumulates."""
+    from bidmat_b200.mat import GMat, GSMat, SMat
+    monkeypatch.setenv("BIDMAT_B200_CHUNK", "32")
+    aroff, acoff, broff, bcoff, croff, ccoff = offs
+    rng = np.random.default_rng(nr + nc + kk)
+    # N: A is (aroff+nr+2) x (acoff+kk+3), S is (broff+kk+4) x (bcoff+nc+5)
+    for transpose in (False, True):
+        srows, scols = ((nc, kk) if transpose else (kk, nc))
+        am, an = aroff + nr + 2, acoff + kk + 3
+        sm, sn = broff + srows + 4, bcoff + scols + 5
+        cm, cn = croff + nr + 1, ccoff + nc + 2
+        jc, ir, data = random_csc(sm, sn, 0.3, rng)
+        a_h = rng.standard_normal((an, am)).astype(np.float32)        # column-major am x an
+        c0 = rng.standard_normal((cn, cm)).astype(np.float32)
+        A = GMat.from_numpy(a_h, cuda_device)
+        C = GMat.from_numpy(c0.copy(), cuda_device)
+        S = GSMat.fromSMat(SMat(sm, sn, jc, ir, data).check(), cuda_device)
+        fn = A.tileMultNT if transpose else A.tileMult
+        fn(nr, nc, kk, aroff, acoff, S, broff, bcoff, C, croff, ccoff)
+        full = SMat(sm, sn, jc, ir, data).full().astype(np.float64).T          # (sm, sn) row-major dense S
+        At = a_h.astype(np.float64).T[aroff:aroff + nr, acoff:acoff + kk]       # nr x kk
+        St = full[broff:broff + srows, bcoff:bcoff + scols]
+        prod = At @ (St.T if transpose else St)                                 # nr x nc
+        want = c0.astype(np.float64).T.copy()                                   # cm x cn
+        want[croff:croff + nr, ccoff:ccoff + nc] += prod
+        got = C.to_numpy().astype(np.float64).T
+        assert np.abs(got - want).max() < 1e-4
+        outside = np.ones_like(want, dtype=bool)
+        outside[croff:croff + nr, ccoff:ccoff + nc] = False
+        assert np.array_equal(got[outside], c0.astype(np.float64).T[outside])
+    with pytest.raises(RuntimeError, match="strays outside"):
+        A.tileMult(nr, nc, kk, aroff, acoff, S, broff, bcoff + 1000, C, croff, ccoff)
