@@ -89,9 +89,12 @@ BIDMAT_B200_API int bidmat_b200_dsmultx_tune(int nrows, int ncols, int nnz, cons
                              int nthreadsy);
 
 /* Stream-ordered forms of the four operations.  They enqueue on `stream` and do
- * not wait.  dsmultT_async takes the row count m of S as a hint (<= 0 when
- * unknown: the library then finds the largest row index itself, which costs a
- * host round trip inside the call). */
+ * not wait for the result.  dsmultT_async takes the row count m of S (it must
+ * exceed every row index in Bir; <= 0 when unknown: the library then finds the
+ * largest row index itself, which costs a host round trip inside the call).  When
+ * the dense operand of dsmultT is much larger than the L2 cache the nonzeros are
+ * processed in column blocks and the call waits once, internally, for the block
+ * boundaries (a few bytes) before it enqueues the rest. */
 BIDMAT_B200_API int bidmat_b200_dsmult_async(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
                              const int *Bir, const int *Bic, float *C, bidmat_stream_t stream);
 BIDMAT_B200_API int bidmat_b200_dsmultT_async(int nrows, int ncols, int nnz, const float *A, const float *Bdata,

@@ -332,3 +332,15 @@ def test_mirror_operators_and_errors(cuda_device):
         assert int(sl.pic.min()) >= 0 and int(sl.pic.max()) < 7
     part = bb * sl
     assert np.abs(part.to_numpy() - d[5:12]).max() < 1e-4
+
+
+@pytest.mark.parametrize("k", [32, 64, 128, 256, 512])
+def test_generic_kernels_at_the_fast_path_heights(cuda_device, k, monkeypatch):
+    """The predicate-free kernels normally take k in {32,...,512}; with the switch
+    below the same shapes run through the general kernels, which must agree."""
+    monkeypatch.setenv("BIDMAT_B200_GENERIC", "1")
+    monkeypatch.setenv("BIDMAT_B200_CHUNK", "64")
+    rng = np.random.default_rng(k)
+    m, n = 120, 80
+    jc, ir, data = random_csc(m, n, 0.25, rng, empty_cols=(5,))
+    check_all_ops(k, m, n, jc, ir, data, cuda_device, rng)
