@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-kernel-timing", action="store_true",
+                    help="do not bracket the kernels with events inside the timed region (no roofline then)")
     ap.add_argument("--emulate-shard", default="", help="R/W: run rank R's shard of a W-way split on one GPU, "
                     "without communication (tuning aid; the JSON line then describes that shard only)")
     return ap.parse_args()
@@ -284,7 +286,7 @@ def run_b200(args, rank, local_rank, world):
             st.run()
         barrier()
         L.bidmat_b200_timing_reset()
-        L.bidmat_b200_timing_enable(1)
+        L.bidmat_b200_timing_enable(0 if args.no_kernel_timing else 1)
         sampler = ClockSampler(physical_index(local_rank))
         launches0 = L.bidmat_b200_launch_count()
         ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
