@@ -385,17 +385,23 @@ def run_b200(args, rank, local_rank, world):
 def run_e2e(args, problem, shard, B_local, dev, world, group, GMat, GSMat, SMat, DDS):
     """Same three operations through the GMat/GSMat operator interface with
     HOST operands: every step uploads A, B and S from pinned memory, runs
-    A*S, DDS and B*^S (+ allreduce) and downloads the three results."""
+    A*S, DDS and B*^S (+ allreduce) and downloads the three results.
+
+    On several GPUs the replicated model A crosses PCIe once (rank 0 uploads it and
+    broadcasts it over NVLink) and the reduced G, identical on every rank, is read
+    back once (by rank 0); S, B, C and P are sharded, each rank moves its own part."""
     import torch.distributed as dist
     k = problem.k
+    rank = dist.get_rank() if world > 1 else 0
     pin = lambda t: t.cpu().pin_memory()
-    hA, hB = pin(problem.A), pin(B_local)
+    hA = pin(problem.A) if rank == 0 else None
+    hB = pin(B_local)
     hjc, hir, hdata = pin(shard.jc), pin(shard.ir), pin(shard.data)
     hC = torch.empty((shard.n, k), dtype=torch.float32).pin_memory()
     hP = torch.empty(shard.nnz, dtype=torch.float32).pin_memory()
-    hG = torch.empty((shard.m, k), dtype=torch.float32).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in (hA, hB, hjc, hir, hdata))
-    d2h = sum(t.numel() * t.element_size() for t in (hC, hP, hG))
+    hG = torch.empty((shard.m, k), dtype=torch.float32).pin_memory() if rank == 0 else None
+    h2d = sum(t.numel() * t.element_size() for t in (hA, hB, hjc, hir, hdata) if t is not None)
+    d2h = sum(t.numel() * t.element_size() for t in (hC, hP, hG) if t is not None)
 
     up = torch.cuda.Stream(device=dev)      # host -> device copies
     down = torch.cuda.Stream(device=dev)    # device -> host copies
@@ -408,11 +414,16 @@ def run_e2e(args, problem, shard, B_local, dev, world, group, GMat, GSMat, SMat,
         # runs in both directions while the next operation computes.
         with torch.cuda.stream(up):
             d_jc, d_ir, d_data = (h.to(dev, non_blocking=True) for h in (hjc, hir, hdata))
-            d_A = hA.to(dev, non_blocking=True)
+            if hA is not None:
+                d_A = hA.to(dev, non_blocking=True)
+            else:
+                d_A = torch.empty((problem.m, k), dtype=torch.float32, device=dev)
             ev_sa = torch.cuda.Event(); ev_sa.record(up)
             d_B = hB.to(dev, non_blocking=True)
             ev_b = torch.cuda.Event(); ev_b.record(up)
         main.wait_event(ev_sa)
+        if group is not None:
+            dist.broadcast(d_A, src=0, group=group)     # the model reaches the other GPUs over NVLink
         A = GMat(d_A)
         S = GSMat.from_csc(shard.m, shard.n, d_jc, d_ir, d_data)
         C = A * S                                   # synchronous, like the BIDMat call
@@ -424,8 +435,9 @@ def run_e2e(args, problem, shard, B_local, dev, world, group, GMat, GSMat, SMat,
         if group is not None:
             dist.all_reduce(G.t, op=dist.ReduceOp.SUM, group=group)
             torch.cuda.current_stream(dev).synchronize()
-        with torch.cuda.stream(down):
-            hG.copy_(G.t, non_blocking=True)
+        if hG is not None:
+            with torch.cuda.stream(down):
+                hG.copy_(G.t, non_blocking=True)
         P = DDS(A, B, S)
         with torch.cuda.stream(down):
             hP.copy_(P.pdata, non_blocking=True)

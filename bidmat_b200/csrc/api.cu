@@ -145,14 +145,15 @@ cudaError_t launch_ga(int k, long long nnz, const S *D, const S *val, const int 
 #define CALL_FAST(LPV, NT, U, MINB)                                                                    \
     ga_chunk_fast_kernel<LPV, NT, U, kFastThreads, MINB><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, D, val, \
                                                                                         gidx, seg, O, part, range, segmask)
-            // k = 256: five CTAs of 128 threads per SM (<= 96 registers) measured 10 % faster
-            // than the 118-register build at four; for the other heights the register cap
-            // costs more in spills than the extra CTA gains (measured at k = 128).
-            if (s.lpv == 8) CALL_FAST(8, 1, 4, 1);
-            else if (s.lpv == 16) CALL_FAST(16, 1, 4, 1);
-            else if (s.nt == 1) CALL_FAST(32, 1, 4, 1);
+            // Last argument: minimum CTAs per SM given to the compiler, 0 = leave it to the
+            // compiler (an explicit 1 makes it take 255 registers and halves the occupancy).
+            // k = 256: five CTAs of 128 threads (<= 96 registers) measured 10 % faster than
+            // the default; at k = 128 the cap costs more in spills than the fifth CTA gains.
+            if (s.lpv == 8) CALL_FAST(8, 1, 4, 0);
+            else if (s.lpv == 16) CALL_FAST(16, 1, 4, 0);
+            else if (s.nt == 1) CALL_FAST(32, 1, 4, 0);
             else if (s.nt == 2) CALL_FAST(32, 2, 2, 5);
-            else CALL_FAST(32, 4, 1, 1);
+            else CALL_FAST(32, 4, 1, 0);
 #undef CALL_FAST
             done = true;
         }

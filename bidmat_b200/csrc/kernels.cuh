@@ -216,7 +216,7 @@ template <int LPV> __device__ __forceinline__ void worker_sync(unsigned mask) {
     __syncwarp(mask);
 }
 
-template <int LPV, int NT, int U, int TPB, int MINB = 1>
+template <int LPV, int NT, int U, int TPB, int MINB = 0>
 __global__ void __launch_bounds__(TPB, MINB)
 ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
                      const float *__restrict__ D, const float *__restrict__ val,
