@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--nccl-allreduce", action="store_true",
+                    help="several GPUs: sum the B*^S partials with NCCL instead of the library's peer-memory kernel")
     ap.add_argument("--no-kernel-timing", action="store_true",
                     help="do not bracket the kernels with events inside the timed region (no roofline then)")
     ap.add_argument("--emulate-shard", default="", help="R/W: run rank R's shard of a W-way split on one GPU, "
@@ -271,7 +273,7 @@ def run_b200(args, rank, local_rank, world):
         shard, bounds = pstep.make_shard(problem, rank, world)
     B_local = problem.B[shard.col0:shard.col1].contiguous()
     stream = torch.cuda.Stream(device=dev)
-    st = pstep.PathStep(k, shard, problem.A, B_local, stream, group)
+    st = pstep.PathStep(k, shard, problem.A, B_local, stream, group, peer_reduce=(world > 1 and not args.nccl_allreduce))
     torch.cuda.synchronize()
 
     def barrier():

@@ -34,6 +34,8 @@ _SIGNATURES = {
     "bidmat_b200_dsmult_noalloc": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dds_async": (_c_int, [_c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dds0_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "bidmat_b200_peer_allreduce_sum": (_c_int, [_c_int, _c_int, ctypes.POINTER(ctypes.c_ulonglong),
+                                                ctypes.c_longlong, _c_int, _vp]),
     "bidmat_b200_expand_jc": (_c_int, [_c_int, _c_int, _vp, _vp, _vp]),
     "bidmat_b200_compress_ic": (_c_int, [_c_int, _c_int, _vp, _vp, _vp]),
     "bidmat_b200_transpose_csc": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

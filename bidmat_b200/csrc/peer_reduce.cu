@@ -1,0 +1,84 @@
+// Sum of the per-GPU partial results of B*^S over NVLink peer memory.
+//
+// Every rank holds a full-size partial G in a buffer its peers can address.
+// Rank r owns the r-th slice of the element range: it reads that slice from
+// every rank's buffer with plain peer loads, adds the values in rank order
+// 0..W-1 (so every GPU ends up with bit-identical sums, whatever the timing),
+// and writes the total back into every rank's buffer with peer stores: a
+// reduce-scatter by pulling and an all-gather by pushing in one kernel, with
+// no float atomics.  The caller must make sure, with its own cross-rank
+// synchronisation, that all partials are complete before the kernel starts on
+// any rank and that nobody touches the buffers until it has finished on all
+// ranks; the kernel itself never waits on another GPU.
+#include <cuda_runtime.h>
+
+#include "../../include/bidmat_b200.h"
+#include "host_common.cuh"
+
+using namespace bidmat;
+
+namespace {
+
+constexpr int kMaxPeers = 16;
+struct PeerPtrs { float *p[kMaxPeers]; };
+
+template <int W>
+__global__ void __launch_bounds__(256)
+peer_sum_kernel(PeerPtrs peers, long long v_begin, long long v_end) {
+    // float4 index range [v_begin, v_end) of this rank's slice
+    constexpr int UNROLL = (W <= 4) ? 4 : 2;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long v0 = v_begin + (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < v_end; v0 += stride * UNROLL) {
+        float4 x[UNROLL][W];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            const long long v = v0 + u * stride;
+#pragma unroll
+            for (int r = 0; r < W; r++)
+                x[u][r] = (v < v_end) ? reinterpret_cast<const float4 *>(peers.p[r])[v] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            const long long v = v0 + u * stride;
+            if (v >= v_end) continue;
+            float4 s = x[u][0];
+#pragma unroll
+            for (int r = 1; r < W; r++) { s.x += x[u][r].x; s.y += x[u][r].y; s.z += x[u][r].z; s.w += x[u][r].w; }
+#pragma unroll
+            for (int r = 0; r < W; r++) reinterpret_cast<float4 *>(peers.p[r])[v] = s;
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int bidmat_b200_peer_allreduce_sum(int world, int rank, const unsigned long long *peer_addresses,
+                                              long long count, int ctas, bidmat_stream_t stream) {
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || count < 0 || !peer_addresses)
+        return (int)cudaErrorInvalidValue;
+    if (count == 0 || world == 1) return 0;
+    if (count % 4 != 0) return (int)cudaErrorInvalidValue;
+    PeerPtrs pp;
+    for (int r = 0; r < kMaxPeers; r++) pp.p[r] = nullptr;
+    for (int r = 0; r < world; r++) {
+        if (peer_addresses[r] == 0 || (peer_addresses[r] & 15ull)) return (int)cudaErrorInvalidValue;
+        pp.p[r] = reinterpret_cast<float *>(peer_addresses[r]);
+    }
+    const long long nvec = count / 4;
+    const long long per = (nvec + world - 1) / world;
+    const long long v_begin = per * rank < nvec ? per * rank : nvec;
+    const long long v_end = v_begin + per < nvec ? v_begin + per : nvec;
+    if (v_end <= v_begin) return 0;
+    // 32 CTAs keep the links busy enough to finish under A*S and DDS on 8 GPUs without
+    // taking many SMs from them (measured: 16 leave the sum exposed, 64 slow the products)
+    if (ctas <= 0) ctas = 32;
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : cudaStreamPerThread;
+    switch (world) {
+        case 2: peer_sum_kernel<2><<<ctas, 256, 0, st>>>(pp, v_begin, v_end); break;
+        case 4: peer_sum_kernel<4><<<ctas, 256, 0, st>>>(pp, v_begin, v_end); break;
+        case 8: peer_sum_kernel<8><<<ctas, 256, 0, st>>>(pp, v_begin, v_end); break;
+        default: return (int)cudaErrorInvalidValue;   // one process per GPU of a 2-, 4- or 8-GPU box
+    }
+    g_launches += 1;
+    return (int)cudaGetLastError();
+}

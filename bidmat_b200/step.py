@@ -10,6 +10,8 @@ src/main/scala/BIDMat/GFunctions.scala:175-203).
 Shards carry local, zero-based column indices, as GSMat.colslice produces
 (src/main/scala/BIDMat/GSMat.scala:77-104).
 """
+import os
+
 import torch
 
 from . import _lib
@@ -55,12 +57,31 @@ class PathStep:
     """A*S, DDS(A,B,S) and B*^S (+ allreduce) on one rank's shard, enqueued on
     one stream through the stream-ordered C ABI."""
 
-    def __init__(self, k, shard, A, B_local, stream, group=None):
+    def __init__(self, k, shard, A, B_local, stream, group=None, peer_reduce=False):
         self.k, self.S, self.A, self.B, self.stream, self.group = int(k), shard, A, B_local, stream, group
         dev = A.device
         self.C = torch.zeros((shard.n, k), dtype=torch.float32, device=dev)
         self.P = torch.zeros(shard.nnz, dtype=torch.float32, device=dev)
-        self.G = torch.zeros((shard.m, k), dtype=torch.float32, device=dev)
+        self.peer = None
+        if group is not None and peer_reduce:
+            # G lives in memory that the other GPUs of the box can address over NVLink;
+            # the sum over ranks is then this library's own kernel, not a library collective.
+            import ctypes
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm
+            self.G = symm.empty((shard.m, k), dtype=torch.float32, device=dev)
+            hdl = symm.rendezvous(self.G, group)
+            world = dist.get_world_size(group)
+            self.peer = {
+                "world": world, "rank": dist.get_rank(group), "handle": hdl,
+                "addrs": (ctypes.c_ulonglong * world)(*[int(a) for a in hdl.buffer_ptrs]),
+                "comm": torch.cuda.Stream(device=dev, priority=-1),
+                "flag": torch.zeros(1, dtype=torch.float32, device=dev),
+                "ctas": int(os.environ.get("BIDMAT_B200_PEER_CTAS", "0")),
+            }
+            self.G.zero_()
+        else:
+            self.G = torch.zeros((shard.m, k), dtype=torch.float32, device=dev)
 
     def dsmult(self):
         S = self.S
@@ -82,12 +103,24 @@ class PathStep:
                                          S.ic.data_ptr(), self.G.data_ptr(), S.m, self.stream.cuda_stream), "dsmultT")
 
     def allreduce_start(self):
-        """Starts the sum of the partials over ranks on NCCL's own stream; the
-        caller's stream is free to run A*S and DDS meanwhile."""
+        """Starts the sum of the partials over ranks off the caller's stream, which
+        is free to run A*S and DDS meanwhile; returns what to wait on."""
         if self.group is None:
             return None
         import torch.distributed as dist
-        return dist.all_reduce(self.G, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        if self.peer is None:
+            return dist.all_reduce(self.G, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        pr = self.peer
+        # Rank synchronisation is a one-element NCCL allreduce before and after (it completes
+        # on a rank only when every rank has reached it in stream order); the data moves in
+        # this library's kernel over peer loads and stores.
+        before = dist.all_reduce(pr["flag"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        with torch.cuda.stream(pr["comm"]):
+            before.wait()
+            _ck(_L.bidmat_b200_peer_allreduce_sum(pr["world"], pr["rank"], pr["addrs"], self.G.numel(), pr["ctas"],
+                                                  pr["comm"].cuda_stream), "peer_allreduce_sum")
+            after = dist.all_reduce(pr["flag"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        return after
 
     def dsmultT(self):
         self.dsmultT_local()

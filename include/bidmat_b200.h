@@ -156,6 +156,20 @@ BIDMAT_B200_API int bidmat_b200_dsmult_noalloc(int nrows, int ncols, int nnz, co
                                                const float *Bdata, const int *Bir, const int *Bic,
                                                float *C, bidmat_stream_t stream);
 
+/* Sum over the GPUs of one box of the per-GPU partial results of B*^S, through
+ * NVLink peer memory instead of a communication library.  peer_addresses[r] is the
+ * device address, valid on the calling GPU, of rank r's buffer of `count` floats
+ * (16-byte aligned, count a multiple of 4; world is 2, 4 or 8).  The calling rank
+ * sums its 1/world slice of all buffers in rank order with peer loads and writes the
+ * total into all buffers with peer stores, so all GPUs end with bit-identical
+ * results.  Stream-ordered on `stream` with `ctas` CTAs of 256 threads (<= 0: 32).
+ * The kernel never waits on another GPU: the caller synchronises the ranks before
+ * (all partials complete) and after (all slices written).
+ * Replaces the role of NCCL.ncclAllReduce in GFunctions.ncclAllReduce
+ *   (src/main/scala/BIDMat/GFunctions.scala:175-203, jni/src/BIDMat_NCCL.cpp:80-90). */
+BIDMAT_B200_API int bidmat_b200_peer_allreduce_sum(int world, int rank, const unsigned long long *peer_addresses,
+                                                   long long count, int ctas, bidmat_stream_t stream);
+
 /* Structure helpers on the device (the steps BIDMat performs around the path
  * with cuSPARSE csr2coo and a host loop: GSMat.fromSMat, GSMat.scala:639, and
  * SparseMat.compressInds, SparseMat.scala:857-868).

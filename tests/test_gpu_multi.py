@@ -1,0 +1,82 @@
+"""Two GPUs (skipped on a single-GPU machine): the library's peer-memory sum of
+the B*^S partials gives the same bits as NCCL's allreduce for two ranks, every
+rank ends with identical G, and the sharded step matches the CPU checker."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from bidmat_b200 import gen, step as pstep
+        p = gen.config2(0.03, seed=5, device=dev)
+        shard, _ = pstep.make_shard(p, rank, world)
+        B_local = p.B[shard.col0:shard.col1].contiguous()
+        stream = torch.cuda.Stream(device=dev)
+        outs = {}
+        with torch.cuda.stream(stream):
+            for mode in (False, True):
+                st = pstep.PathStep(p.k, shard, p.A, B_local, stream, dist.group.WORLD, peer_reduce=mode)
+                for _ in range(2):        # twice: the buffers are reused from step to step
+                    st.run()
+                torch.cuda.synchronize()
+                dist.barrier()
+                outs[mode] = st.G.clone()
+        same_bits = torch.equal(outs[False].view(torch.int32), outs[True].view(torch.int32))
+        other = outs[True].clone()
+        dist.broadcast(other, src=0)
+        same_across_ranks = torch.equal(other.view(torch.int32), outs[True].view(torch.int32))
+        if rank == 0:
+            import oracle
+            from util import RTOL_DSMULTT
+            jc, ir, data = p.jc.cpu().numpy(), p.ir.cpu().numpy(), p.data.cpu().numpy()
+            Bh = p.B.cpu().numpy()
+            want = oracle.dsmultT(Bh, data, ir, jc, p.m)
+            _, scale = oracle.dsmultT_f64(Bh, data, ir, jc, p.m)
+            ok = bool(np.all(np.abs(outs[True].cpu().numpy().astype(np.float64) - want) <= RTOL_DSMULTT * scale + 1e-30))
+            q.put((same_bits, same_across_ranks, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.timeout(600)
+def test_peer_memory_sum_matches_nccl_on_two_gpus():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(500)
+        assert p.exitcode == 0
+    same_bits, same_across_ranks, ok = q.get(timeout=10)
+    assert same_bits, "peer-memory sum and NCCL allreduce differ for two ranks"
+    assert same_across_ranks, "ranks ended with different G"
+    assert ok, "sharded B*^S differs from the CPU checker"
