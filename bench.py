@@ -376,6 +376,8 @@ def run_b200(args, rank, local_rank, world):
         "dtype": "f32", "data": "synthetic", "config": workload_config(problem, args, world),
         "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline, "e2e": e2e,
         "allreduce_exposed_ms": op_ms_max["allreduce_exposed"] if world > 1 else 0.0,
+        "allreduce": (None if world == 1 else
+                      "library kernel over NVLink peer memory" if st.peer is not None else "NCCL"),
     }
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args, problem)

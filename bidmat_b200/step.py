@@ -66,22 +66,36 @@ class PathStep:
         if group is not None and peer_reduce:
             # G lives in memory that the other GPUs of the box can address over NVLink;
             # the sum over ranks is then this library's own kernel, not a library collective.
-            import ctypes
-            import torch.distributed as dist
-            import torch.distributed._symmetric_memory as symm
-            self.G = symm.empty((shard.m, k), dtype=torch.float32, device=dev)
-            hdl = symm.rendezvous(self.G, group)
-            world = dist.get_world_size(group)
-            self.peer = {
-                "world": world, "rank": dist.get_rank(group), "handle": hdl,
-                "addrs": (ctypes.c_ulonglong * world)(*[int(a) for a in hdl.buffer_ptrs]),
-                "comm": torch.cuda.Stream(device=dev, priority=-1),
-                "flag": torch.zeros(1, dtype=torch.float32, device=dev),
-                "ctas": int(os.environ.get("BIDMAT_B200_PEER_CTAS", "0")),
-            }
-            self.G.zero_()
-        else:
+            # If peer-addressable memory cannot be set up, NCCL sums the partials instead
+            # (said on stderr; self.peer stays None).
+            try:
+                self._setup_peer_memory(shard, k, dev, group)
+            except Exception as e:   # pragma: no cover - depends on the machine
+                import sys
+                print("bidmat_b200: peer-addressable memory unavailable (%s); summing B*^S partials with NCCL"
+                      % (str(e).splitlines()[0] if str(e) else type(e).__name__), file=sys.stderr)
+                self.peer = None
+        if self.peer is None:
             self.G = torch.zeros((shard.m, k), dtype=torch.float32, device=dev)
+
+    def _setup_peer_memory(self, shard, k, dev, group):
+        import ctypes
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        G = symm.empty((shard.m, k), dtype=torch.float32, device=dev)
+        hdl = symm.rendezvous(G, group)
+        world = dist.get_world_size(group)
+        if world not in (2, 4, 8):
+            raise RuntimeError("peer-memory sum supports 2, 4 or 8 GPUs")
+        self.G = G
+        self.peer = {
+            "world": world, "rank": dist.get_rank(group), "handle": hdl,
+            "addrs": (ctypes.c_ulonglong * world)(*[int(a) for a in hdl.buffer_ptrs]),
+            "comm": torch.cuda.Stream(device=dev, priority=-1),
+            "flag": torch.zeros(1, dtype=torch.float32, device=dev),
+            "ctas": int(os.environ.get("BIDMAT_B200_PEER_CTAS", "0")),
+        }
+        self.G.zero_()
 
     def dsmult(self):
         S = self.S
