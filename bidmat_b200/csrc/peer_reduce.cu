@@ -69,9 +69,10 @@ extern "C" int bidmat_b200_peer_allreduce_sum(int world, int rank, const unsigne
     const long long v_begin = per * rank < nvec ? per * rank : nvec;
     const long long v_end = v_begin + per < nvec ? v_begin + per : nvec;
     if (v_end <= v_begin) return 0;
-    // 32 CTAs keep the links busy enough to finish under A*S and DDS on 8 GPUs without
-    // taking many SMs from them (measured: 16 leave the sum exposed, 64 slow the products)
-    if (ctas <= 0) ctas = 32;
+    // Default CTA count: enough to finish underneath A*S and DDS, which shrink with the
+    // number of GPUs, without taking many SMs from them (measured on 8 GPUs: 16 leave the
+    // sum exposed, 64 slow the products; on 2 GPUs 32 leave it exposed, 64 hide it).
+    if (ctas <= 0) ctas = (world <= 2) ? 64 : (world <= 4) ? 48 : 32;
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : cudaStreamPerThread;
     switch (world) {
         case 2: peer_sum_kernel<2><<<ctas, 256, 0, st>>>(pp, v_begin, v_end); break;

@@ -162,7 +162,8 @@ BIDMAT_B200_API int bidmat_b200_dsmult_noalloc(int nrows, int ncols, int nnz, co
  * (16-byte aligned, count a multiple of 4; world is 2, 4 or 8).  The calling rank
  * sums its 1/world slice of all buffers in rank order with peer loads and writes the
  * total into all buffers with peer stores, so all GPUs end with bit-identical
- * results.  Stream-ordered on `stream` with `ctas` CTAs of 256 threads (<= 0: 32).
+ * results.  Stream-ordered on `stream` with `ctas` CTAs of 256 threads (<= 0: 64 / 48 / 32
+ * for 2 / 4 / 8 GPUs).
  * The kernel never waits on another GPU: the caller synchronises the ranks before
  * (all partials complete) and after (all slices written).
  * Replaces the role of NCCL.ncclAllReduce in GFunctions.ncclAllReduce
