@@ -54,7 +54,8 @@ inline int pick_chunk(long long nnz, int lpv) {
     long long c;
     if (forced > 0) c = forced;
     else {
-        c = (nnz + kTargetChunks - 1) / kTargetChunks;
+        const long long target = env_int("BIDMAT_B200_TARGET_CHUNKS", (int)kTargetChunks);
+        c = (nnz + target - 1) / target;
         if (c < 64) c = 64;
         if (c > 4096) c = 4096;
     }
@@ -68,7 +69,8 @@ inline long long max_chunks_for(long long nnz, int lpv) {
     const int chunk_all = pick_chunk(nnz, lpv);
     long long cap = (nnz + chunk_all - 1) / chunk_all;
     long long by64 = (nnz + 63) / 64 + 1;
-    long long alt = by64 < kTargetChunks + 1 ? by64 : kTargetChunks + 1;
+    const long long target = env_int("BIDMAT_B200_TARGET_CHUNKS", (int)kTargetChunks);
+    long long alt = by64 < target + 1 ? by64 : target + 1;
     return alt > cap ? alt : cap;
 }
 

@@ -123,10 +123,14 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
 }
 
 // One worker per chunk.  The worker whose chunk holds the START of a run that
-// leaves the chunk to the right finds the chunk in which the run ends (binary
-// search: seg is non-decreasing as unsigned keys), adds the stored pieces in
-// chunk order, with the loads issued four chunks ahead of the adds, and adds the
-// total to O.  Every other worker returns.
+// leaves the chunk to the right adds the stored pieces of the run in chunk
+// order and adds the total to O.  Every other worker returns.
+// Most runs that cross a boundary end in the very next chunk, so that case is
+// one memory round trip: the piece leaving chunk c, the piece entering chunk
+// c+1, the "does it go on" test and the current output column are independent
+// loads issued together.  Longer runs (hot rows or long columns) continue
+// four chunks per round trip.  The kernel is kept small in registers: it is
+// latency bound and lives on occupancy.
 template <typename S, int VEC, int LPV, int NT>
 __global__ void __launch_bounds__(kThreads)
 ga_fixup_kernel(int k, long long nnz, int chunk, long long nchunks,
@@ -143,51 +147,65 @@ ga_fixup_kernel(int k, long long nnz, int chunk, long long nchunks,
     const long long j1 = j0 + chunk;
     if (j1 >= hi) return;
     const int s = __ldg(seg + j1 - 1);
-    if (__ldg(seg + j1) != s) return;                       // nothing leaves to the right
-    if (j0 > lo && __ldg(seg + j0 - 1) == s) return;        // the run started further left
-
-    // last position of the run: largest e in [j1, hi) with seg[e] == s
-    long long a = j1, b = hi;                               // invariant: seg[a] == s, seg[b] > s or b == hi
-    while (b - a > 1) {
-        const long long mid = (a + b) >> 1;
-        if ((unsigned)__ldg(seg + mid) <= (unsigned)s) a = mid; else b = mid;
-    }
-    const long long dend = (a - lo) / chunk;                // chunk holding the end of the run
+    const int next = __ldg(seg + j1);
+    const int prev = (j0 > lo) ? __ldg(seg + j0 - 1) : ~s;
+    if (next != s) return;                                  // nothing leaves to the right
+    if (prev == s) return;                                  // the run started further left
 
     const int ktile = blockIdx.y * (LPV * NT * VEC);
+    const long long last = (hi - lo - 1) / chunk;           // index of the last chunk of the slice
+    // does the run go on after chunk d (i.e. chunk d is all s and chunk d+1 starts with s)?
+    // Both index loads are issued unconditionally (at a clamped, always valid position):
+    // a short-circuit would make the second load wait for the first and serialise the walk.
+    auto goes_on = [&](long long d) -> bool {
+        const long long dc = d < last ? d : last - 1;        // last >= 1 here
+        const long long dj1 = lo + (dc + 1) * (long long)chunk;
+        const int a = __ldg(seg + dj1 - 1);
+        const int b = __ldg(seg + dj1);
+        return (d < last) & (a == s) & (b == s);
+    };
     int eoff[NT];
     bool eok[NT];
-    VT tot[NT];
+    VT tot[NT], x1[NT], old[NT];
+    S *o = O + (size_t)((unsigned)s & segmask) * ld_o;
 #pragma unroll
     for (int t = 0; t < NT; t++) {
         eoff[t] = ktile + (lane + t * LPV) * VEC;
         eok[t] = eoff[t] < k;
         tot[t] = eok[t] ? V::ld(part + ((size_t)c * 2 + 1) * k + eoff[t]) : V::zero();
+        x1[t] = eok[t] ? V::ld(part + ((size_t)(c + 1) * 2) * k + eoff[t]) : V::zero();
+        old[t] = eok[t] ? V::ld(o + eoff[t]) : V::zero();
     }
+    bool more = goes_on(c + 1);
+#pragma unroll
+    for (int t = 0; t < NT; t++) V::add(tot[t], x1[t]);
+
     constexpr int PF = 4;
-    for (long long d = c + 1; d <= dend; d += PF) {
+    for (long long d = c + 2; more; d += PF) {
         VT x[PF][NT];
+        bool g[PF];
 #pragma unroll
         for (int q = 0; q < PF; q++) {
-            const long long dd = (d + q <= dend) ? d + q : dend;
+            const long long dd = (d + q <= last) ? d + q : last;
             const S *p = part + (size_t)dd * 2 * k;
 #pragma unroll
             for (int t = 0; t < NT; t++) x[q][t] = eok[t] ? V::ld(p + eoff[t]) : V::zero();
+            g[q] = goes_on(d + q);
         }
 #pragma unroll
-        for (int q = 0; q < PF; q++)
-            if (d + q <= dend) {
+        for (int q = 0; q < PF; q++) {
+            if (more) {
 #pragma unroll
                 for (int t = 0; t < NT; t++) V::add(tot[t], x[q][t]);
+                more = g[q];
             }
+        }
     }
-    S *o = O + (size_t)((unsigned)s & segmask) * ld_o;
 #pragma unroll
     for (int t = 0; t < NT; t++)
         if (eok[t]) {
-            VT old = V::ld(o + eoff[t]);
-            V::add(old, tot[t]);
-            V::st(o + eoff[t], old);
+            V::add(old[t], tot[t]);
+            V::st(o + eoff[t], old[t]);
         }
 }
 
