@@ -276,7 +276,9 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     };
 
     int cur = __ldg(seg + j0);
-    bool head_open = (j0 > lo) && (__ldg(seg + j0 - 1) == cur);
+    const int seg_before = (j0 > lo) ? __ldg(seg + j0 - 1) : ~cur;
+    const int seg_after = (j1 < hi) ? __ldg(seg + j1) : 0;      // fetched now, needed at the very end
+    bool head_open = (j0 > lo) && (seg_before == cur);
     float4 acc[NT];
     float4 oldv[NT];   // current contents of the output column of the run, fetched when the run starts
 #pragma unroll
@@ -363,7 +365,7 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
         }
         worker_sync<LPV>(mask);   // everyone is done with this buffer before it is staged again
     }
-    const bool tail_open = (j1 < hi) && (__ldg(seg + j1) == cur);
+    const bool tail_open = (j1 < hi) && (seg_after == cur);
     flush(tail_open);
 }
 
