@@ -57,7 +57,10 @@ def _time(fn, stream, reps, warmup):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", type=int, required=True, choices=[1, 2, 3, 5])
+    ap.add_argument("--config", type=int, default=2, choices=[1, 2, 3, 5])
+    ap.add_argument("--extras", action="store_true",
+                    help="time the operations around the path (transpose, sums, edge operators, tiles, fp64 twins) "
+                         "on the LDA-shaped configuration at --scale (one GPU)")
     ap.add_argument("--k", type=int, nargs="*", default=[32, 64, 128, 256, 512])
     ap.add_argument("--scale", type=float, default=1.0)
     ap.add_argument("--seed", type=int, default=0)
@@ -79,6 +82,8 @@ def main():
     from . import gen, step as pstep
     peak, peak_src = _peak()
     stream = torch.cuda.Stream(device=dev)
+    if args.extras:
+        return extras(args, dev, stream, peak, peak_src)
 
     if args.config == 3:
         problems = [(lambda kk=kk: gen.config3(kk, args.scale, args.seed, dev)) for kk in args.k]
@@ -132,6 +137,72 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
+
+
+def extras(args, dev, stream, peak, peak_src):
+    """Operations either side of the path, on device-resident operands, through the
+    synchronous C ABI (each call ends with a stream synchronisation, as in BIDMat)."""
+    from . import _lib, gen
+    from .mat import GMat, GSMat
+    L = _lib.lib
+    p = gen.config2(args.scale, args.seed, dev)
+    S = GSMat.from_csc(p.m, p.n, p.jc, p.ir, p.data)
+    k, nnz, m, n = p.k, p.nnz, p.m, p.n
+    A, B = GMat(p.A), GMat(p.B)
+    rowv = torch.rand(n, device=dev) + 0.5
+    colv = torch.rand(m, device=dev) + 0.5
+    vals = p.data.clone()
+    sums_c = torch.zeros(n, device=dev)
+    sums_r = torch.zeros(m, device=dev)
+    A64, B64 = p.A.double(), p.B.double()
+    d64 = p.data.double()
+    C64 = torch.zeros((n, k), dtype=torch.float64, device=dev)
+    G64 = torch.zeros((m, k), dtype=torch.float64, device=dev)
+    P64 = torch.zeros(nnz, dtype=torch.float64, device=dev)
+    Ct = torch.zeros((n, k), device=dev)
+    half_r, half_c = m // 2, n // 2
+    ptr = lambda t: t.data_ptr()
+
+    def ck(e):
+        if e != 0:
+            raise RuntimeError(_lib.error_string(e))
+
+    cases = [
+        ("transpose (GSMat.t)", lambda: S.t, nnz * 24.0, None),
+        ("spsum columns", lambda: ck(L.bidmat_b200_spsum(m, n, nnz, ptr(S.pir), ptr(S.pic), ptr(S.pdata), ptr(sums_c), 1)),
+         nnz * 8.0 + n * 8.0, None),
+        ("spsum rows", lambda: ck(L.bidmat_b200_spsum(m, n, nnz, ptr(S.pir), ptr(S.pic), ptr(S.pdata), ptr(sums_r), 2)),
+         nnz * 8.0 + m * 8.0, None),
+        ("sdoprow (*@ row vector)", lambda: ck(L.bidmat_b200_sdoprow(m, n, nnz, ptr(vals), ptr(S.pic), ptr(rowv), n, 2)),
+         nnz * 12.0, None),
+        ("sdopcol (*@ column vector)", lambda: ck(L.bidmat_b200_sdopcol(m, n, nnz, ptr(vals), ptr(S.pir), ptr(colv), m, 2)),
+         nnz * 16.0, None),
+        ("dsmultTile (whole matrix as one tile)",
+         lambda: ck(L.bidmat_b200_dsmultTile(k, n, m, nnz, A.pdata, k, ptr(S.pdata), ptr(S.pir), ptr(S.pic), 0, 0, ptr(Ct), k, 0)),
+         _alg_bytes("A*S", k, nnz, n, m), 2.0 * k * nnz),
+        ("dsmultTile (lower-right quarter)",
+         lambda: ck(L.bidmat_b200_dsmultTile(k, n - half_c, m - half_r, nnz, A.pdata + 4 * k * half_r, k, ptr(S.pdata),
+                                             ptr(S.pir), ptr(S.pic), half_r, half_c, ptr(Ct) + 4 * k * half_c, k, 0)),
+         None, None),
+        ("A*S fp64", lambda: ck(L.bidmat_b200_dsmult_f64(k, n, nnz, ptr(A64), ptr(d64), ptr(S.pir), ptr(S.pic), ptr(C64))),
+         nnz * (8.0 * k + 16) + n * 16.0 * k, 2.0 * k * nnz),
+        ("DDS fp64", lambda: ck(L.bidmat_b200_dds_f64(k, nnz, ptr(A64), ptr(B64), ptr(S.pir), ptr(S.pic), ptr(P64))),
+         nnz * (8.0 * k + 24) + n * 8.0 * k, 2.0 * k * nnz),
+        ("B*^S fp64", lambda: ck(L.bidmat_b200_dsmultT_f64(k, n, nnz, ptr(B64), ptr(d64), ptr(S.pir), ptr(S.pic), ptr(G64))),
+         nnz * (8.0 * k + 16) + m * 16.0 * k, 2.0 * k * nnz),
+    ]
+    for name, fn, nbytes, flops in cases:
+        ms = _time(fn, torch.cuda.current_stream(dev), args.reps, args.warmup)
+        out = {"config": p.name, "op": name, "k": k, "m": m, "n": n, "nnz": nnz, "n_gpus": 1, "ms": ms,
+               "scale": args.scale, "seed": args.seed}
+        if nbytes:
+            out["algorithmic_gb"] = nbytes / 1e9
+            out["roofline_frac"] = nbytes / (ms * 1e-3) / 1e9 / peak
+            out["peak_gbs"], out["peak_source"] = peak, peak_src
+        if flops:
+            out["gflops"] = flops / (ms * 1e-3) / 1e9
+        print(json.dumps(out), flush=True)
+    return 0
 
 
 if __name__ == "__main__":
