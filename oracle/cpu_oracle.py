@@ -22,14 +22,35 @@ _F64P = ctypes.POINTER(ctypes.c_double)
 _I32P = ctypes.POINTER(ctypes.c_int32)
 
 _lib = None
+_libs = {}
 _ref = None
 _ref_tried = False
+_ref_gpu = None
+_ref_gpu_tried = False
+_variant = "plain"
+
+
+def use_native(on=True):
+    """Selects which build of spdense_oracle.c the functions below call: the plain
+    x86-64 build (default) or the -O3 -march=native build made on this machine.
+    Both give the same bits (contraction is off in both); the native one is what
+    the benchmark times.  Returns the variant actually in use."""
+    global _variant, _lib
+    want = "native" if on else "plain"
+    if want == "native" and _build.build_oracle_native() is None:
+        want = "plain"
+    _variant = want
+    _lib = None
+    return want
 
 
 def _load():
     global _lib
+    if _lib is None and _variant in _libs:
+        _lib = _libs[_variant]
     if _lib is None:
-        _lib = ctypes.CDLL(_build.build_oracle())
+        _lib = ctypes.CDLL(_build.build_oracle_native() if _variant == "native" else _build.build_oracle())
+        _libs[_variant] = _lib
         for name in ("oracle_dsmult", "oracle_dsmultT"):
             getattr(_lib, name).argtypes = [ctypes.c_int, ctypes.c_int, _F32P, _F32P, _I32P, _I32P,
                                             _F32P, ctypes.c_int]
@@ -305,3 +326,62 @@ def ref_dmcsrm(B, data, ir, jc, m, out=None):
         out = np.zeros((m, k), dtype=np.float64)
     lib.ref_dmcsrm(k, n, pB, pd, pir, pjc, out.ctypes.data_as(_F64P))
     return out
+
+
+# ---- the reference's own CUDA launchers (jni/src/Arith.cu), compiled for sm_100a.
+# Arguments are device addresses as integers; each call synchronises the legacy
+# default stream and returns a cudaError_t (0 = success), as the launchers do.
+def _load_ref_gpu():
+    global _ref_gpu, _ref_gpu_tried
+    if not _ref_gpu_tried:
+        _ref_gpu_tried = True
+        path = _build.build_reference_gpu()
+        if path and os.path.exists(path):
+            vp, ci = ctypes.c_void_p, ctypes.c_int
+            _ref_gpu = ctypes.CDLL(path)
+            _ref_gpu.ref_gpu_dsmult.argtypes = [ci, ci, ci, vp, vp, vp, vp, vp]
+            _ref_gpu.ref_gpu_dsmultT.argtypes = [ci, ci, ci, vp, vp, vp, vp, vp]
+            _ref_gpu.ref_gpu_dds.argtypes = [ci, ci, vp, vp, vp, vp, vp]
+            _ref_gpu.ref_gpu_dds0.argtypes = [ci, ci, vp, vp, vp, vp, vp]
+            _ref_gpu.ref_gpu_spsum.argtypes = [ci, ci, ci, vp, vp, vp, vp, ci]
+            for name in ("ref_gpu_dsmult", "ref_gpu_dsmultT", "ref_gpu_dds", "ref_gpu_dds0", "ref_gpu_spsum"):
+                getattr(_ref_gpu, name).restype = ci
+    return _ref_gpu
+
+
+def ref_gpu_available():
+    return _load_ref_gpu() is not None
+
+
+def _ref_gpu_call(name, *args):
+    lib = _load_ref_gpu()
+    if lib is None:
+        raise RuntimeError("reference build oracle/_ref/libarith_ref.so is not available")
+    err = getattr(lib, name)(*args)
+    if err != 0:
+        raise RuntimeError("%s returned CUDA error %d" % (name, err))
+
+
+def ref_gpu_dsmult(k, n, nnz, A, data, ir, ic, C):
+    """dsmult (jni/src/Arith.cu:46-60): C += A * S, float atomics."""
+    _ref_gpu_call("ref_gpu_dsmult", k, n, nnz, A, data, ir, ic, C)
+
+
+def ref_gpu_dsmultT(k, n, nnz, B, data, ir, ic, C):
+    """dsmultT (jni/src/Arith.cu:234-248): C += B * S^T, float atomics."""
+    _ref_gpu_call("ref_gpu_dsmultT", k, n, nnz, B, data, ir, ic, C)
+
+
+def ref_gpu_dds(k, nnz, A, B, ir, ic, P):
+    """dds (jni/src/Arith.cu:381-389): P[j] += <A[:, ir[j]], B[:, ic[j]]>."""
+    _ref_gpu_call("ref_gpu_dds", k, nnz, A, B, ir, ic, P)
+
+
+def ref_gpu_dds0(k, n, A, B, ir, jc, P):
+    """dds0 (jni/src/Arith.cu:391-399); k must be 1024."""
+    _ref_gpu_call("ref_gpu_dds0", k, n, A, B, ir, jc, P)
+
+
+def ref_gpu_spsum(m, n, nnz, ir, ic, P, B, which):
+    """spsum (jni/src/Arith.cu:267-277): which == 1 column sums, else row sums."""
+    _ref_gpu_call("ref_gpu_spsum", m, n, nnz, ir, ic, P, B, which)

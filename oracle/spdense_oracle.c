@@ -12,10 +12,18 @@
  *                           from the reference tree (see oracle/build.py).
  *   B*^S  (oracle_dsmultT)  pinned: bit-identical to smcsrm
  *                           (jni/src/BIDMat_SPBLAS.c:397-427), same recipe.
- *   DDS   (oracle_dds)      PARITY UNPINNED: the reference has no C twin and no
- *                           test or golden vector for DDS; the loop below
- *                           follows the Scala source only
- *                           (src/main/scala/BIDMat/MatFunctions.scala:1594-1618).
+ *   DDS   (oracle_dds)      arithmetic pinned: bit-identical to smcscm called
+ *                           with a one-row dense operand, which adds v[j]*a[ir[j]]
+ *                           in j order from a stored 0
+ *                           (jni/src/BIDMat_SPBLAS.c:376-388), i.e. the
+ *                           "dsum += a(k)*b(k)" loop of DDShelper
+ *                           (src/main/scala/BIDMat/MatFunctions.scala:1603-1607);
+ *                           stored as tests/golden/dds_ref_vectors.npz.  Which
+ *                           (row, column) pair a nonzero samples is pinned by the
+ *                           Scala source (MatFunctions.scala:1594-1618) and, in
+ *                           the GPU tests, by the reference's own CUDA dds
+ *                           (jni/src/Arith.cu:291-310, 381-389) compiled for
+ *                           sm_100a; the reference has no test of DDS.
  *
  * All dense matrices are column-major fp32 with leading dimension k; S is CSC
  * with 0-based int32 jc[n+1], ir[nnz] and fp32 data[nnz].  Arithmetic is strict

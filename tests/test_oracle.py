@@ -145,3 +145,71 @@ def test_double_precision_oracle_matches_live_reference_build(k, m, n, dens):
                           oracle.ref_dmcsrm(B, data, ir, jc, m, out=G0.copy()))
     ic = oracle.uncompress_inds(jc)
     assert np.allclose(oracle.dds_d(A, B, ir, jc), np.einsum("ij,ij->i", A[ir], B[ic]), rtol=1e-13, atol=1e-13)
+
+
+# ---- DDS: arithmetic pinned to the reference's compiled smcscm / dmcscm loop
+DDS_GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "dds_ref_vectors.npz")
+
+
+def dds_golden_cases():
+    z = np.load(DDS_GOLDEN)
+    return z, sorted({k.split("/")[0] for k in z.files})
+
+
+@pytest.mark.parametrize("name", dds_golden_cases()[1])
+def test_dds_oracle_matches_reference_golden_bit_exact(name):
+    """The stored values were produced by the reference's own smcscm / dmcscm loop
+    (one-row dense operand, column = B[:, c]; tests/golden/make_golden.py), which adds
+    the products in the order DDShelper does (MatFunctions.scala:1603-1607)."""
+    z, _ = dds_golden_cases()
+    g = {k.split("/")[1]: z[k] for k in z.files if k.startswith(name + "/")}
+    for nthreads in (1, 4):
+        P = oracle.dds(g["A"], g["B"], g["ir"], g["jc"], nthreads=nthreads)
+        assert np.array_equal(P.view(np.uint32), g["P"].view(np.uint32))
+    P64 = oracle.dds_d(g["A"].astype(np.float64), g["B"].astype(np.float64), g["ir"], g["jc"])
+    assert np.array_equal(P64.view(np.uint64), g["P64"].view(np.uint64))
+
+
+@pytest.mark.skipif(not oracle.ref_available(), reason="reference build not present")
+@pytest.mark.parametrize("k", [1, 7, 128, 256, 512])
+def test_dds_oracle_matches_live_reference_smcscm(k):
+    """smcscm with M = 1 (BIDMat_SPBLAS.c:376-388): C[0,c] = sum_j v[j]*a[ir[j]] in j
+    order from a stored 0 is the dot product of DDShelper, bit for bit."""
+    sys_path_golden = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(sys_path_golden, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    rng = np.random.default_rng(77 + k)
+    m, n = 11, 9
+    jc, ir, _ = random_csc(m, n, 0.5, rng, empty_cols=(4,))
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((n, k)).astype(np.float32)
+    want = mg.dds_through_smcscm(A, B, ir, jc)
+    got = oracle.dds(A, B, ir, jc)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    A64, B64 = rng.standard_normal((m, k)), rng.standard_normal((n, k))
+    want64 = mg.dds_through_smcscm(A64, B64, ir, jc, f64=True)
+    assert np.array_equal(oracle.dds_d(A64, B64, ir, jc).view(np.uint64), want64.view(np.uint64))
+
+
+def test_native_build_of_the_oracle_gives_the_same_bits():
+    """The -O3 -march=native build (what the benchmark times) against the plain build."""
+    rng = np.random.default_rng(31)
+    k, m, n = 256, 300, 120
+    jc, ir, data = random_csc(m, n, 0.2, rng, empty_cols=(5,))
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((n, k)).astype(np.float32)
+    C0 = rng.standard_normal((n, k)).astype(np.float32)
+    try:
+        oracle.use_native(False)
+        plain = (oracle.dsmult(A, data, ir, jc, out=C0.copy(), nthreads=3), oracle.dsmultT(B, data, ir, jc, m, nthreads=3),
+                 oracle.dds(A, B, ir, jc, nthreads=3))
+        if oracle.use_native(True) != "native":
+            pytest.skip("no native build on this machine")
+        native = (oracle.dsmult(A, data, ir, jc, out=C0.copy(), nthreads=3), oracle.dsmultT(B, data, ir, jc, m, nthreads=3),
+                  oracle.dds(A, B, ir, jc, nthreads=3))
+    finally:
+        oracle.use_native(False)
+    for p, q in zip(plain, native):
+        assert np.array_equal(p.view(np.uint32), q.view(np.uint32))
