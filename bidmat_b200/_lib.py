@@ -31,11 +31,22 @@ _SIGNATURES = {
     "bidmat_b200_dsmult_f64_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dsmultT_f64_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _c_int, _vp]),
     "bidmat_b200_dds_f64_async": (_c_int, [_c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "bidmat_b200_dsmultT_plan_create": (_c_int, [_c_int, _c_int, _c_int, _c_int, _vp, _vp, _c_int, _vp,
+                                                 ctypes.POINTER(_vp)]),
+    "bidmat_b200_dsmultT_planned": (_c_int, [_vp, _c_int, _c_int, _c_int, _vp, _vp, _vp, _c_int, _vp]),
+    "bidmat_b200_dsmultT_planned_f64": (_c_int, [_vp, _c_int, _c_int, _c_int, _vp, _vp, _vp, _c_int, _vp]),
+    "bidmat_b200_plan_verify": (_c_int, [_vp, _c_int, _c_int, _vp, _vp, _vp]),
+    "bidmat_b200_plan_info": (_c_int, [_vp, ctypes.POINTER(ctypes.c_longlong), _c_int]),
+    "bidmat_b200_plan_touched_rows": (_c_int, [_vp, _vp, _vp]),
+    "bidmat_b200_plan_destroy": (_c_int, [_vp]),
+    "bidmat_b200_set_workspace_limit": (_c_int, [ctypes.c_longlong]),
     "bidmat_b200_dsmult_noalloc": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dds_async": (_c_int, [_c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dds0_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_peer_allreduce_sum": (_c_int, [_c_int, _c_int, ctypes.POINTER(ctypes.c_ulonglong),
                                                 ctypes.c_longlong, _c_int, _vp]),
+    "bidmat_b200_peer_allreduce_sum_rows": (_c_int, [_c_int, _c_int, ctypes.POINTER(ctypes.c_ulonglong), _c_int,
+                                                     ctypes.c_longlong, _vp, _c_int, _vp]),
     "bidmat_b200_expand_jc": (_c_int, [_c_int, _c_int, _vp, _vp, _vp]),
     "bidmat_b200_compress_ic": (_c_int, [_c_int, _c_int, _vp, _vp, _vp]),
     "bidmat_b200_transpose_csc": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -13,279 +13,15 @@
 #include <vector>
 
 #include "../../include/bidmat_b200.h"
-#include "kernels.cuh"
+#include "launchers.cuh"
 #include "structure_kernels.cuh"
-#include "rowsort.cuh"
 #include "edgeops.cuh"
 #include "tile_compact.cuh"
-#include "host_common.cuh"
 
 using namespace bidmat;
 
 namespace {
 
-
-// ------------------------------------------------------------------ timing
-// Optional per-kernel timing for the benchmark: when enabled, the launchers
-// bracket their main kernels with CUDA events on the launching stream.
-struct TimedSpan { const char *label; cudaEvent_t a, b; };
-std::atomic<int> g_timing{0};
-std::mutex g_span_mu;
-std::vector<TimedSpan> g_spans;
-
-struct ScopedSpan {
-    cudaStream_t st;
-    TimedSpan span{nullptr, nullptr, nullptr};
-    ScopedSpan(const char *label, cudaStream_t s) : st(s) {
-        if (!g_timing.load()) return;
-        if (cudaEventCreate(&span.a) != cudaSuccess || cudaEventCreate(&span.b) != cudaSuccess) return;
-        span.label = label;
-        cudaEventRecord(span.a, st);
-    }
-    ~ScopedSpan() {
-        if (!span.label) return;
-        cudaEventRecord(span.b, st);
-        std::lock_guard<std::mutex> g(g_span_mu);
-        g_spans.push_back(span);
-    }
-};
-
-// ------------------------------------------------------------------ workspace
-// One grow-only scratch buffer per device.  Calls on one device are serialised
-// by the mutex for their host part and ordered on the device by an event, so
-// two streams can never use the buffer at the same time.
-struct Workspace {
-    std::mutex mu;
-    void *ptr = nullptr;
-    size_t bytes = 0;
-    cudaEvent_t last_use = nullptr;
-};
-constexpr int kMaxDevices = 64;
-Workspace g_ws[kMaxDevices];
-
-struct WorkspaceLease {
-    Workspace *ws = nullptr;
-    cudaStream_t stream = nullptr;
-    char *base = nullptr;
-    size_t used = 0;
-    cudaError_t err = cudaSuccess;
-
-    WorkspaceLease(size_t bytes, cudaStream_t s) : stream(s) {
-        int dev = 0;
-        err = cudaGetDevice(&dev);
-        if (err != cudaSuccess) return;
-        if (dev < 0 || dev >= kMaxDevices) { err = cudaErrorInvalidDevice; return; }
-        ws = &g_ws[dev];
-        ws->mu.lock();
-        if (ws->last_use == nullptr) {
-            err = cudaEventCreateWithFlags(&ws->last_use, cudaEventDisableTiming);
-            if (err != cudaSuccess) return;
-        } else {
-            err = cudaStreamWaitEvent(stream, ws->last_use, 0);
-            if (err != cudaSuccess) return;
-        }
-        if (bytes > ws->bytes) {
-            if (ws->ptr) {
-                err = cudaDeviceSynchronize();
-                if (err != cudaSuccess) return;
-                cudaFree(ws->ptr);
-                ws->ptr = nullptr;
-                ws->bytes = 0;
-            }
-            size_t want = bytes + bytes / 8 + (1u << 20);
-            err = cudaMalloc(&ws->ptr, want);
-            if (err != cudaSuccess) { ws->ptr = nullptr; return; }
-            ws->bytes = want;
-        }
-        base = static_cast<char *>(ws->ptr);
-    }
-    template <typename T> T *take(size_t count) {
-        size_t off = (used + 255) & ~size_t(255);
-        used = off + count * sizeof(T);
-        return reinterpret_cast<T *>(base + off);
-    }
-    ~WorkspaceLease() {
-        if (ws) {
-            if (ws->last_use) cudaEventRecord(ws->last_use, stream);
-            ws->mu.unlock();
-        }
-    }
-};
-
-inline size_t pad256(size_t b) { return (b + 255) & ~size_t(255); }
-
-// O[:, seg[j]] += val[j] * D[:, gidx[j]] with `part` holding 2*nchunks*k floats.
-constexpr int kFastThreads = 128;
-
-// k = 4*lpv*nt exactly and 16-byte aligned operands: the predicate-free kernels apply.
-bool fast_shape(int k, const Shape &s) { return s.vec == 4 && s.tiles == 1 && k == 4 * s.lpv * s.nt; }
-
-// `count` nonzeros are processed: the whole list (range == nullptr, count == nnz) or
-// the slice [range[0], range[1]) read on the device.  The output column of a
-// nonzero is seg & segmask.  S is float or double; the predicate-free fast
-// kernels exist for float only.
-template <typename S>
-cudaError_t launch_ga(int k, long long nnz, const S *D, const S *val, const int *gidx,
-                      const int *seg, S *O, S *part, int chunk, const Shape &s,
-                      cudaStream_t st, const char *label, long long count = -1,
-                      const int *range = nullptr, unsigned segmask = 0xffffffffu, int ld_d = 0, int ld_o = 0) {
-    constexpr int kWideVec = 16 / (int)sizeof(S);
-    if (ld_d <= 0) ld_d = k;     // leading dimensions: k unless the operands are tiles of larger matrices
-    if (ld_o <= 0) ld_o = k;
-    if (count < 0) count = nnz;
-    if (count == 0) return cudaSuccess;
-    const long long nchunks = (count + chunk - 1) / chunk;
-    dim3 grid(blocks_for(nchunks, s.lpv), s.tiles, 1);
-    bool done = false;
-    if constexpr (std::is_same<S, float>::value) {
-        if (fast_shape(k, s) && ld_d == k && ld_o == k && !env_int("BIDMAT_B200_GENERIC", 0)) {
-            const int wpb = kFastThreads / s.lpv;
-            dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
-            ScopedSpan sp(label, st);
-#define CALL_FAST(LPV, NT, U, MINB)                                                                    \
-    ga_chunk_fast_kernel<LPV, NT, U, kFastThreads, MINB><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, D, val, \
-                                                                                        gidx, seg, O, part, range, segmask)
-            // Last argument: minimum CTAs per SM given to the compiler, 0 = leave it to the
-            // compiler (an explicit 1 makes it take 255 registers and halves the occupancy).
-            // k = 256: five CTAs of 128 threads (<= 96 registers) measured 10 % faster than
-            // the default; at k = 128 the cap costs more in spills than the fifth CTA gains.
-            if (s.lpv == 8) CALL_FAST(8, 1, 4, 0);
-            else if (s.lpv == 16) CALL_FAST(16, 1, 4, 0);
-            else if (s.nt == 1) CALL_FAST(32, 1, 4, 0);
-            else if (s.nt == 2) CALL_FAST(32, 2, 2, 5);
-            else CALL_FAST(32, 4, 1, 0);
-#undef CALL_FAST
-            done = true;
-        }
-    }
-    if (!done) {
-#define CALL_GA(VEC, LPV, NT)                                                                   \
-    {                                                                                           \
-        ScopedSpan sp(label, st);                                                               \
-        ga_chunk_kernel<S, VEC, LPV, NT, 4><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, D, val, \
-                                                                       gidx, seg, O, part, range, \
-                                                                       segmask, ld_d, ld_o);    \
-    }
-        DISPATCH_SHAPE(s, CALL_GA);
-#undef CALL_GA
-    }
-    if (nchunks > 1) {
-        ScopedSpan sp("ga_fixup", st);
-#define CALL_FIX(VEC, LPV, NT) \
-    ga_fixup_kernel<S, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, seg, O, part, range, segmask, ld_o);
-        DISPATCH_SHAPE(s, CALL_FIX);
-#undef CALL_FIX
-    }
-    g_launches += (nchunks > 1) ? 2 : 1;
-    return cudaGetLastError();
-}
-
-template <typename S, bool ACCUM>
-cudaError_t launch_dds(int k, long long nnz, const S *A, const S *B, const int *ir,
-                       const int *ic, S *P, cudaStream_t st) {
-    constexpr int kWideVec = 16 / (int)sizeof(S);
-    const Shape s = pick_shape(k, is16(A) && is16(B), kWideVec);
-    const int chunk = pick_chunk(nnz, s.lpv);
-    const long long nchunks = (nnz + chunk - 1) / chunk;
-    dim3 grid(blocks_for(nchunks, s.lpv), 1, 1);
-    ScopedSpan sp("dds_chunk", st);
-    bool done = false;
-    if constexpr (std::is_same<S, float>::value) {
-        if (fast_shape(k, s) && s.lpv == 32 && s.nt <= 2 && !env_int("BIDMAT_B200_GENERIC", 0)) {
-            const int wpb = kFastThreads / 32;
-            dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
-            if (s.nt == 1)
-                dds_chunk_fast_kernel<1, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
-            else
-                dds_chunk_fast_kernel<2, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
-            done = true;
-        }
-    }
-    if (!done) {
-#define CALL_DDS(VEC, LPV, NT)                                                                  \
-    dds_chunk_kernel<S, VEC, LPV, NT, 4, ACCUM><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, A, B, \
-                                                                           ir, ic, P);
-        DISPATCH_SHAPE(s, CALL_DDS);
-#undef CALL_DDS
-    }
-    g_launches += 1;
-    return cudaGetLastError();
-}
-
-// Sorts the nonzero list (ir, ic, v) by key (see rowsort.cuh) in `passes` 8-bit
-// passes.  Intermediate results ping-pong between the two scratch buffer sets;
-// when out_* are given the last pass writes there.  Returns the index of the
-// scratch set holding the result, or -1 when it went to out_*.
-template <typename S>
-int run_rowsort(int nnz, int passes, SortKeySpec ks, const int *ir, const int *ic, const S *v,
-                unsigned *const keys[2], int *const cols[2], S *const vals[2], unsigned *out_keys,
-                int *out_cols, S *out_vals, int *counts, int *totals, cudaStream_t st) {
-    static std::once_flag smem_once[kMaxDevices];
-    {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev < 0 || dev >= kMaxDevices) dev = 0;
-        std::call_once(smem_once[dev], [] {
-            cudaFuncSetAttribute(sort_scatter_kernel<true, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem<S>));
-            cudaFuncSetAttribute(sort_scatter_kernel<false, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SortSmem<S>));
-        });
-    }
-    const int ntiles = (int)(((size_t)nnz + kSortTile - 1) / kSortTile);
-    const int tps = (ntiles + kSortScanSegs - 1) / kSortScanSegs;   // tiles per scan segment
-    int cur = 0;   // scratch set holding the output of the last pass
-    ScopedSpan sp("dsmultT_rowsort", st);
-    for (int p = 0; p < passes; p++) {
-        const int shift = 8 * p;
-        const bool to_user = (p == passes - 1) && out_keys != nullptr;
-        const int out = (p == 0) ? 0 : 1 - cur;
-        unsigned *ko = to_user ? out_keys : keys[out];
-        int *co = to_user ? out_cols : cols[out];
-        S *vo = to_user ? out_vals : vals[out];
-        {
-            ScopedSpan sp1("sort_hist", st);
-            if (p == 0) {
-                sort_hist_kernel<true><<<ntiles, kSortThreads, 0, st>>>(nnz, ntiles, shift, ks, nullptr, ir, ic, counts);
-            } else {
-                sort_hist_kernel<false><<<ntiles, kSortThreads, 0, st>>>(nnz, ntiles, shift, ks, keys[cur], nullptr, nullptr, counts);
-            }
-        }
-        {
-            ScopedSpan sp2("sort_scan", st);
-            sort_scan_kernel<<<dim3(kSortScanSegs, 256), kSortThreads, 0, st>>>(ntiles, tps, counts, totals);
-            sort_digit_base_kernel<<<1, 256, 0, st>>>(totals);
-        }
-        {
-            ScopedSpan sp3("sort_scatter", st);
-            if (p == 0) {
-                sort_scatter_kernel<true, S><<<ntiles, kSortThreads, sizeof(SortSmem<S>), st>>>(
-                    nnz, ntiles, shift, ks, nullptr, ir, ic, v, counts, totals, tps, ko, co, vo);
-            } else {
-                sort_scatter_kernel<false, S><<<ntiles, kSortThreads, sizeof(SortSmem<S>), st>>>(
-                    nnz, ntiles, shift, ks, keys[cur], nullptr, cols[cur], vals[cur], counts, totals, tps, ko, co, vo);
-            }
-        }
-        g_launches += 4;
-        cur = to_user ? -1 : out;
-    }
-    return cur;
-}
-
-inline cudaStream_t as_stream(bidmat_stream_t s) {
-    return s ? static_cast<cudaStream_t>(s) : cudaStreamPerThread;
-}
-
-inline int finish_sync(cudaError_t err, cudaStream_t st) {
-    if (err != cudaSuccess) return (int)err;
-    err = cudaStreamSynchronize(st);
-    if (err != cudaSuccess) return (int)err;
-    return (int)cudaGetLastError();
-}
-
-int ceil_log2(unsigned long long v) {  // smallest b with 2^b >= v (v >= 1)
-    int b = 0;
-    while ((1ull << b) < v) b++;
-    return b;
-}
 
 template <typename S>
 int dsmult_impl(int nrows, int ncols, int nnz, const S *A, const S *Bdata,
@@ -312,35 +48,6 @@ int dsmultT_impl(int nrows, int ncols, int nnz, const S *A, const S *Bdata,
     cudaStream_t st = st_in;
     const size_t n = (size_t)nnz;
     const Shape s = pick_shape(nrows, is16(A) && is16(C), 16 / (int)sizeof(S));
-
-    // Column blocks: when the dense operand is much larger than L2, the nonzeros
-    // are ordered by (column block, row) so that the gathers of one block stay
-    // L2-resident; blocks are then processed one after the other.
-    const size_t dense_bytes = (size_t)ncols * (size_t)nrows * sizeof(S);
-    size_t l2_bytes = 96u << 20;
-    {
-        int dev = 0, l2 = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, dev) == cudaSuccess && l2 > 0)
-            l2_bytes = (size_t)l2;
-    }
-    // block = half of L2 unless BIDMAT_B200_COLBLOCK_MB says otherwise (0 disables);
-    // an operand up to 1.5 x L2 is left in one piece (measured: splitting a 128 MB
-    // operand in two costs more in extra output passes than it gains in hits).
-    const int block_mb = env_int("BIDMAT_B200_COLBLOCK_MB", -1);
-    const size_t block_bytes = block_mb >= 0 ? ((size_t)block_mb << 20) : l2_bytes / 2;
-    int colshift = 31;
-    const int forced_cols = env_int("BIDMAT_B200_COLBLOCK_COLS", 0);   // tests force tiny blocks
-    if (forced_cols > 0) {
-        colshift = 0;
-        while ((2 << colshift) <= forced_cols) colshift++;
-    } else if (block_bytes > 0 && dense_bytes > l2_bytes + l2_bytes / 2) {
-        // columns per block: the power of two nearest to block_bytes / column bytes
-        size_t cols_per_block = block_bytes / ((size_t)nrows * sizeof(S));
-        colshift = 0;
-        while ((2ull << colshift) <= cols_per_block) colshift++;
-        if (cols_per_block * 1000 >= (1ull << colshift) * 1414) colshift++;
-    }
 
     const int ntiles = (int)((n + kSortTile - 1) / kSortTile);
     size_t need = 4 * pad256(n * 4) + 2 * pad256(n * sizeof(S)) + pad256((size_t)256 * ntiles * 4) + 4 * pad256(4096) + pad256(256 * kSortScanSegs * 4) + 4096;
@@ -377,32 +84,13 @@ int dsmultT_impl(int nrows, int ncols, int nnz, const S *A, const S *Bdata,
         if (h < 0) return (int)cudaErrorInvalidValue;
         rowbits = ceil_log2((unsigned long long)h + 1);
     }
-    if (rowbits < 1) rowbits = 1;
-    if (rowbits > 31) return (int)cudaErrorInvalidValue;
-    int nblocks = (colshift >= 31) ? 1 : (((ncols - 1) >> colshift) + 1);
-    while (nblocks > 1 && (rowbits + ceil_log2((unsigned long long)nblocks) > 32 || nblocks > 1023)) {
-        colshift++;
-        nblocks = ((ncols - 1) >> colshift) + 1;
-    }
-    // Is splitting worth it?  Unsplit, about every gather misses L2: nnz*4k bytes of
-    // DRAM reads.  Split, B is read once but every block re-reads and re-writes the
-    // output rows it touches (at most all 2^rowbits of them) and the sort may need
-    // one more pass over 24 bytes per nonzero.  Split only for a clear win; tests
-    // that force a block size skip the model.
-    if (nblocks > 1 && forced_cols <= 0) {
-        const double colbytes = (double)sizeof(S) * nrows;
-        const double rows = (m_hint > 0) ? (double)m_hint : (double)(1ull << rowbits);
-        const double unsplit = (double)nnz * colbytes;
-        const int extra_pass = ((rowbits + ceil_log2((unsigned long long)nblocks) + 7) / 8) - ((rowbits + 7) / 8);
-        const double split = (double)dense_bytes + (double)nblocks * rows * 2.0 * colbytes +
-                             2.0 * (8.0 + sizeof(S)) * nnz * extra_pass;
-        if (split > 0.6 * unsplit) nblocks = 1;
-    }
-    if (nblocks <= 1) { colshift = 31; nblocks = 1; }
-    const int keybits = rowbits + (nblocks > 1 ? ceil_log2((unsigned long long)nblocks) : 0);
-    const int passes = (keybits + 7) / 8;
-    const SortKeySpec ks{colshift, rowbits};
-    const unsigned rowmask = (rowbits >= 32) ? 0xffffffffu : ((1u << rowbits) - 1u);
+    BlockLayout lay;
+    if (!choose_block_layout(nrows, ncols, nnz, sizeof(S), rowbits, m_hint > 0 ? (double)m_hint : 0.0, 32, &lay))
+        return (int)cudaErrorInvalidValue;
+    const int nblocks = lay.nblocks, passes = lay.passes;
+    rowbits = lay.rowbits;
+    const SortKeySpec ks{lay.colshift, lay.rowbits};
+    const unsigned rowmask = lay.rowmask;
 
     const int cur = run_rowsort<S>(nnz, passes, ks, Bir, Bic, Bdata, keys, cols, vals, nullptr, nullptr, nullptr, counts,
                                 totals, st);
@@ -793,8 +481,11 @@ int bidmat_b200_dsmultTile(int nr, int nc, int kk, int nnz, const float *A, int 
 long long bidmat_b200_workspace_bytes(void) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
-    std::lock_guard<std::mutex> g(g_ws[dev].mu);
-    return (long long)g_ws[dev].bytes;
+    std::lock_guard<std::mutex> g(g_pools[dev].mu);
+    if (!g_pools[dev].pool) return 0;
+    unsigned long long reserved = 0;
+    if (cudaMemPoolGetAttribute(g_pools[dev].pool, cudaMemPoolAttrReservedMemCurrent, &reserved) != cudaSuccess) return 0;
+    return (long long)reserved;
 }
 
 int bidmat_b200_release_workspace(void) {
@@ -802,14 +493,20 @@ int bidmat_b200_release_workspace(void) {
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return (int)err;
     if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
-    std::lock_guard<std::mutex> g(g_ws[dev].mu);
-    if (g_ws[dev].ptr) {
-        err = cudaDeviceSynchronize();
-        cudaFree(g_ws[dev].ptr);
-        g_ws[dev].ptr = nullptr;
-        g_ws[dev].bytes = 0;
-    }
-    return (int)err;
+    std::lock_guard<std::mutex> g(g_pools[dev].mu);
+    if (!g_pools[dev].pool) return 0;
+    // blocks still leased by calls in flight stay; everything already returned goes back to the driver
+    return (int)cudaMemPoolTrimTo(g_pools[dev].pool, 0);
+}
+
+int bidmat_b200_set_workspace_limit(long long bytes) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return (int)err;
+    if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+    if (bytes < 0) return (int)cudaErrorInvalidValue;
+    g_pools[dev].limit.store(bytes);
+    return 0;
 }
 
 long long bidmat_b200_launch_count(void) { return g_launches.load(); }

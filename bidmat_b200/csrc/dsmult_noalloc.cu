@@ -89,10 +89,35 @@ extern "C" int bidmat_b200_dsmult_noalloc(int nrows, int ncols, int nnz, const f
     dim3 grid(blocks_for(nchunks, s.lpv), s.tiles, 1);
     const int ichunk = (int)chunk;
     constexpr int kWideVec = 4;
+    // Dense heights 32..512 with 16-byte aligned operands take the same predicate-free
+    // gather kernel as bidmat_b200_dsmult_async (it needs nothing but `part` either).
+    if (s.vec == 4 && s.tiles == 1 && nrows == 4 * s.lpv * s.nt && !env_int("BIDMAT_B200_GENERIC", 0)) {
+        constexpr int kFast = 128;
+        const int wpb = kFast / s.lpv;
+        dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
+#define CALL_FAST_NOALLOC(LPV, NT, U, MINB)                                                             \
+    ga_chunk_fast_kernel<LPV, NT, U, kFast, MINB><<<fgrid, kFast, 0, st>>>(nnz, ichunk, nchunks, A, Bdata, Bir, Bic, C, \
+                                                                        part, nullptr, 0xffffffffu)
+        if (s.lpv == 8) CALL_FAST_NOALLOC(8, 1, 4, 0);
+        else if (s.lpv == 16) CALL_FAST_NOALLOC(16, 1, 4, 0);
+        else if (s.nt == 1) CALL_FAST_NOALLOC(32, 1, 4, 0);
+        else if (s.nt == 2) CALL_FAST_NOALLOC(32, 2, 2, 5);
+        else CALL_FAST_NOALLOC(32, 4, 1, 0);
+#undef CALL_FAST_NOALLOC
+        if (nchunks > 1) {
+#define CALL_FIX_NOALLOC(VEC, LPV, NT)                                                                  \
+    ga_fixup_kernel<float, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(nrows, nnz, ichunk, nchunks, Bic, C, part, nullptr, \
+                                                                    0xffffffffu, nrows);
+            DISPATCH_SHAPE(s, CALL_FIX_NOALLOC);
+#undef CALL_FIX_NOALLOC
+        }
+        g_launches += (nchunks > 1) ? 2 : 1;
+        return (int)cudaGetLastError();
+    }
 #define CALL_GA_NOALLOC(VEC, LPV, NT)                                                                  \
     ga_chunk_kernel<float, VEC, LPV, NT, 4><<<grid, kThreads, 0, st>>>(nrows, nnz, ichunk, nchunks, A, Bdata, \
                                                                 Bir, Bic, C, part, nullptr,           \
-                                                                0xffffffffu, nrows, nrows);            \
+                                                                0xffffffffu, nrows, nrows, nullptr, 0u); \
     if (nchunks > 1)                                                                                   \
         ga_fixup_kernel<float, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(nrows, nnz, ichunk, nchunks, Bic, C, part, nullptr, \
                                                                         0xffffffffu, nrows);

@@ -30,9 +30,16 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
                 const S *__restrict__ D, const S *__restrict__ val,
                 const int *__restrict__ gidx, const int *__restrict__ seg,
                 S *__restrict__ O, S *__restrict__ part,
-                const int *__restrict__ range, unsigned segmask, int ld_d, int ld_o) {
+                const int *__restrict__ range, unsigned segmask, int ld_d, int ld_o,
+                const int4 *__restrict__ desc, unsigned storebit) {
     // ld_d / ld_o: distance in elements between consecutive columns of D and O
     // (k for whole matrices, larger for tiles of bigger matrices)
+    // desc: when given, chunk c is desc[c] = {first nonzero, end, slot of the piece
+    // entering from the left or -1, slot of the piece leaving to the right, -1 when
+    // nothing leaves, -2 when the whole chunk is one run that goes on} (a prepared
+    // plan, see plan.cu) instead of the regular grid of `chunk` nonzeros.
+    // storebit: a run whose segment value has this bit set overwrites its output
+    // column instead of adding to it (0: always add).
     typedef Vec<S, VEC> V;
     typedef typename V::T VT;
     const int lane = threadIdx.x & (LPV - 1);
@@ -51,13 +58,25 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
 
     // [lo, hi) is the slice of the nonzero list this launch works on (the whole
     // list unless `range` points at two offsets); chunks are counted from lo.
-    const long long lo = range ? (long long)__ldg(range) : 0;
-    const long long hi = range ? (long long)__ldg(range + 1) : nnz;
-    const long long j0 = lo + c * (long long)chunk;
-    if (j0 >= hi) return;
-    const long long j1 = (j0 + chunk < hi) ? j0 + chunk : hi;
-    int cur = __ldg(seg + j0);
-    bool head_open = (j0 > lo) && (__ldg(seg + j0 - 1) == cur);
+    long long lo = 0, hi = nnz, j0, j1;
+    long long hslot = c * 2, tslot = c * 2 + 1;
+    int cur;
+    bool head_open;
+    int tail_code = 0;                 // plan: -1 nothing leaves to the right, else something does
+    if (desc) {
+        const int4 dc = __ldg(desc + c);
+        j0 = dc.x; j1 = dc.y; hslot = dc.z; tslot = dc.w; tail_code = dc.w;
+        cur = __ldg(seg + j0);
+        head_open = dc.z >= 0;
+    } else {
+        lo = range ? (long long)__ldg(range) : 0;
+        hi = range ? (long long)__ldg(range + 1) : nnz;
+        j0 = lo + c * (long long)chunk;
+        if (j0 >= hi) return;
+        j1 = (j0 + chunk < hi) ? j0 + chunk : hi;
+        cur = __ldg(seg + j0);
+        head_open = (j0 > lo) && (__ldg(seg + j0 - 1) == cur);
+    }
 
     VT acc[NT];
 #pragma unroll
@@ -66,15 +85,20 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
     auto flush = [&](bool tail_open) {
         if (!head_open && !tail_open) {
             S *o = O + (size_t)((unsigned)cur & segmask) * ld_o;
+            const bool overwrite = ((unsigned)cur & storebit) != 0u;
 #pragma unroll
             for (int t = 0; t < NT; t++)
                 if (eok[t]) {
-                    VT old = V::ld(o + eoff[t]);
-                    V::add(old, acc[t]);
-                    V::st(o + eoff[t], old);
+                    if (overwrite) {
+                        V::st(o + eoff[t], acc[t]);
+                    } else {
+                        VT old = V::ld(o + eoff[t]);
+                        V::add(old, acc[t]);
+                        V::st(o + eoff[t], old);
+                    }
                 }
         } else {
-            S *p = part + ((size_t)c * 2 + (head_open ? 0 : 1)) * k;
+            S *p = part + (size_t)(head_open ? hslot : tslot) * k;
 #pragma unroll
             for (int t = 0; t < NT; t++)
                 if (eok[t]) V::st(p + eoff[t], acc[t]);
@@ -118,7 +142,7 @@ ga_chunk_kernel(int k, long long nnz, int chunk, long long nchunks,
             }
         }
     }
-    const bool tail_open = (j1 < hi) && (__ldg(seg + j1) == cur);
+    const bool tail_open = desc ? (tail_code != -1) : ((j1 < hi) && (__ldg(seg + j1) == cur));
     flush(tail_open);
 }
 

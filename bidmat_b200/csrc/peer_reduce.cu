@@ -50,7 +50,85 @@ peer_sum_kernel(PeerPtrs peers, long long v_begin, long long v_end) {
     }
 }
 
+// Same sum when every rank knows which rows (columns of k floats of the k x m result)
+// each rank wrote: touched[r * words + w] bit b set = rank r wrote row 32*w + b.  A
+// rank's row is only read when that rank wrote it, so ranks need not clear the rows
+// they did not write (they may hold anything, e.g. the previous sum), and rows that
+// nobody wrote are set to zero.  Requires k % 4 == 0.
+template <int W>
+__global__ void __launch_bounds__(256)
+peer_sum_rows_kernel(PeerPtrs peers, long long v_begin, long long v_end, int vec_per_row,
+                     const unsigned *__restrict__ touched, long long words) {
+    constexpr int UNROLL = (W <= 4) ? 4 : 2;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long v0 = v_begin + (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < v_end; v0 += stride * UNROLL) {
+        float4 x[UNROLL][W];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            const long long v = v0 + u * stride;
+            const long long row = (v < v_end ? v : v_begin) / vec_per_row;
+            const long long w = row >> 5;
+            const int bit = (int)(row & 31);
+#pragma unroll
+            for (int r = 0; r < W; r++) {
+                const bool wrote = (__ldg(touched + r * words + w) >> bit) & 1u;
+                x[u][r] = (v < v_end && wrote) ? reinterpret_cast<const float4 *>(peers.p[r])[v]
+                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            const long long v = v0 + u * stride;
+            if (v >= v_end) continue;
+            float4 s = x[u][0];
+#pragma unroll
+            for (int r = 1; r < W; r++) { s.x += x[u][r].x; s.y += x[u][r].y; s.z += x[u][r].z; s.w += x[u][r].w; }
+#pragma unroll
+            for (int r = 0; r < W; r++) reinterpret_cast<float4 *>(peers.p[r])[v] = s;
+        }
+    }
+}
+
+int peer_args(int world, int rank, const unsigned long long *peer_addresses, long long count, PeerPtrs *pp,
+              long long *v_begin, long long *v_end) {
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || count < 0 || !peer_addresses)
+        return (int)cudaErrorInvalidValue;
+    if (count % 4 != 0) return (int)cudaErrorInvalidValue;
+    for (int r = 0; r < kMaxPeers; r++) pp->p[r] = nullptr;
+    for (int r = 0; r < world; r++) {
+        if (peer_addresses[r] == 0 || (peer_addresses[r] & 15ull)) return (int)cudaErrorInvalidValue;
+        pp->p[r] = reinterpret_cast<float *>(peer_addresses[r]);
+    }
+    const long long nvec = count / 4;
+    const long long per = (nvec + world - 1) / world;
+    *v_begin = per * rank < nvec ? per * rank : nvec;
+    *v_end = *v_begin + per < nvec ? *v_begin + per : nvec;
+    return 0;
+}
+
 }  // namespace
+
+extern "C" int bidmat_b200_peer_allreduce_sum_rows(int world, int rank, const unsigned long long *peer_addresses,
+                                                   int k, long long m, const unsigned *touched, int ctas,
+                                                   bidmat_stream_t stream) {
+    if (k <= 0 || k % 4 != 0 || m < 0 || !touched) return (int)cudaErrorInvalidValue;
+    PeerPtrs pp;
+    long long v_begin = 0, v_end = 0;
+    const int bad = peer_args(world, rank, peer_addresses, (long long)k * m, &pp, &v_begin, &v_end);
+    if (bad) return bad;
+    if (m == 0 || world == 1 || v_end <= v_begin) return 0;
+    if (ctas <= 0) ctas = (world <= 2) ? 64 : (world <= 4) ? 48 : 32;
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : cudaStreamPerThread;
+    const long long words = (m + 31) / 32;
+    switch (world) {
+        case 2: peer_sum_rows_kernel<2><<<ctas, 256, 0, st>>>(pp, v_begin, v_end, k / 4, touched, words); break;
+        case 4: peer_sum_rows_kernel<4><<<ctas, 256, 0, st>>>(pp, v_begin, v_end, k / 4, touched, words); break;
+        case 8: peer_sum_rows_kernel<8><<<ctas, 256, 0, st>>>(pp, v_begin, v_end, k / 4, touched, words); break;
+        default: return (int)cudaErrorInvalidValue;
+    }
+    g_launches += 1;
+    return (int)cudaGetLastError();
+}
 
 extern "C" int bidmat_b200_peer_allreduce_sum(int world, int rank, const unsigned long long *peer_addresses,
                                               long long count, int ctas, bidmat_stream_t stream) {

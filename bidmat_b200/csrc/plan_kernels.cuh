@@ -1,0 +1,356 @@
+// Kernels of the prepared ("planned") transposed product B*^S.
+//
+// A plan holds, for one sparse structure, the nonzero list sorted by
+// (column block, row) with the source column and the original position of every
+// nonzero, cut into chunks whose boundaries sit on row boundaries wherever a run
+// of equal rows is shorter than a chunk.  A call then only has to bring the
+// values into sorted order (one gather through the stored positions) and run the
+// gather-accumulate kernel block after block: no sort, no host round trip.
+// Runs longer than a chunk are split; their pieces go to numbered slots and one
+// fix-up launch after the last block adds them, in chunk order, to the output.
+#pragma once
+#include "kernels.cuh"
+
+namespace bidmat {
+
+// ---------------------------------------------------------------------------
+// Chunk boundaries.  The nonzeros [lo, hi) of one column block are sorted by key.
+// Nominal boundaries sit at lo + c*T; boundary c is moved back to the start of
+// the run of equal keys that contains it, unless that run began at or before the
+// previous nominal boundary (then the run is longer than a chunk and is cut at
+// the nominal position).  Every chunk is non-empty and shorter than 2T.
+// Outputs, for c in [0, nch]: start[c], the key at start[c] (first[c]) and the key
+// just before it (prev[c]); c = nch describes the end of the block.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+plan_bounds_kernel(int lo, int hi, int T, int nch, const unsigned *__restrict__ keys,
+                   int *__restrict__ start, unsigned *__restrict__ first, unsigned *__restrict__ prev) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c > nch) return;
+    int b;
+    if (c == 0) b = lo;
+    else if (c == nch) b = hi;
+    else {
+        const int p = lo + c * T;                 // < hi because nch = ceil((hi-lo)/T)
+        const unsigned key = __ldg(keys + p);
+        int a = lo, z = p;                        // first position in [lo, p] holding `key`
+        while (a < z) {
+            const int mid = (a + z) >> 1;
+            if (__ldg(keys + mid) < key) a = mid + 1; else z = mid;
+        }
+        b = (a > lo + (c - 1) * T) ? a : p;
+    }
+    start[c] = b;
+    first[c] = (b < hi) ? __ldg(keys + b) : 0xffffffffu;
+    prev[c] = (b > lo) ? __ldg(keys + b - 1) : 0xffffffffu;
+}
+
+// vals[j] = data[perm[j]]: the values of a call, brought into the plan's order.
+// mismatch (optional): set to 1 when the structure handed in with the call is not
+// the one the plan was made for (row or column of a nonzero differs).
+template <typename S>
+__global__ void __launch_bounds__(256)
+plan_permute_kernel(long long n, const int *__restrict__ perm, const S *__restrict__ data, S *__restrict__ vals) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += stride)
+        vals[j] = __ldg(data + __ldg(perm + j));
+}
+
+// Exact check that (ir, ic) is the structure a plan was built from: every sorted
+// entry must name the row and column found at its stored source position.
+__global__ void __launch_bounds__(256)
+plan_verify_kernel(long long n, const int *__restrict__ perm, const unsigned *__restrict__ keys,
+                   const int *__restrict__ cols, unsigned rowmask, const int *__restrict__ ir,
+                   const int *__restrict__ ic, int *__restrict__ mismatch) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    bool bad = false;
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += stride) {
+        const int p = __ldg(perm + j);
+        bad |= ((unsigned)__ldg(ir + p) != (__ldg(keys + j) & rowmask)) | (__ldg(ic + p) != __ldg(cols + j));
+    }
+    if (bad) *mismatch = 1;
+}
+
+// first_block[row] = lowest column block that holds a nonzero of the row (integer
+// atomicMin at plan time only); rows nobody names keep kNoBlock (what a byte-wise
+// memset with 0x7f leaves).
+constexpr int kNoBlock = 0x7f7f7f7f;
+__global__ void __launch_bounds__(256)
+plan_first_block_kernel(long long n, const unsigned *__restrict__ keys, int rowbits, unsigned rowmask,
+                        int *__restrict__ first_block) {
+    const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    const unsigned key = __ldg(keys + j);
+    // only the first nonzero of a run needs to vote
+    if (j > 0 && __ldg(keys + j - 1) == key) return;
+    atomicMin(first_block + (key & rowmask), (int)(key >> rowbits));
+}
+
+// Marks (bit 31 of the key) every nonzero that belongs to the first block of its
+// row: in overwrite mode the run holding it stores instead of adding.  Rows whose
+// first run is split over chunks (listed in `no_store`, 1 per row) are left
+// unmarked: the call clears them and accumulates.
+__global__ void __launch_bounds__(256)
+plan_mark_first_kernel(long long n, unsigned *__restrict__ keys, int rowbits, unsigned rowmask,
+                       const int *__restrict__ first_block, const unsigned char *__restrict__ no_store) {
+    const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    const unsigned key = keys[j];
+    const unsigned row = key & rowmask;
+    if ((int)(key >> rowbits) == first_block[row] && !no_store[row]) keys[j] = key | 0x80000000u;
+}
+
+// touched[w] bit b = row 32*w + b is named by at least one nonzero.
+__global__ void __launch_bounds__(256)
+plan_touched_kernel(int m, const int *__restrict__ first_block, unsigned *__restrict__ touched) {
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool t = (row < m) && (first_block[row] != kNoBlock);
+    const unsigned bal = __ballot_sync(0xffffffffu, t);
+    if ((threadIdx.x & 31) == 0 && row < m) touched[row >> 5] = bal;
+}
+
+// Zeroes the output columns listed in rows[] (one worker of 32 lanes per column).
+template <typename S>
+__global__ void __launch_bounds__(256)
+plan_clear_rows_kernel(int k, int nrows_listed, const int *__restrict__ rows, S *__restrict__ O) {
+    const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (w >= nrows_listed) return;
+    S *o = O + (size_t)__ldg(rows + w) * k;
+    for (int i = threadIdx.x & 31; i < k; i += 32) o[i] = (S)0;
+}
+
+__device__ __forceinline__ void prefetch_l2(const void *p) {
+    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p));
+}
+
+// ---------------------------------------------------------------------------
+// Gather-accumulate over the chunks of a plan, dense heights k = 4*LPV*NT with
+// 16-byte aligned operands (the shapes of ga_chunk_fast_kernel, which this kernel
+// follows: cp.async-staged (index, value, segment) triples, gathers U columns
+// ahead of the FMAs, read half of the output's read-modify-write issued when a
+// run starts).  Differences:
+//   * chunk c of the launch is desc[c] = {first nonzero, end, slot of the piece
+//     entering from the left or -1, slot of the piece leaving to the right / -1
+//     nothing leaves / -2 the whole chunk is one run that goes on};
+//   * the rows of the transposed product are short runs (often a single nonzero),
+//     so the read of the output column would be a DRAM round trip per run on the
+//     critical path: while batch b is processed, the output columns of the runs
+//     that START in batch b+1 are prefetched into L2 (no registers held);
+//   * a run whose segment value has `storebit` set overwrites its output column.
+// ---------------------------------------------------------------------------
+template <int LPV, int NT, int U, int TPB, int MINB, bool PREFETCH>
+__global__ void __launch_bounds__(TPB, MINB)
+ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
+                    const float *__restrict__ D, const float *__restrict__ val,
+                    const int *__restrict__ gidx, const int *__restrict__ seg,
+                    float *__restrict__ O, float *__restrict__ part, unsigned segmask, unsigned storebit) {
+    constexpr int K = 4 * LPV * NT;
+    constexpr int WPB = TPB / LPV;
+    constexpr int G = LPV / U;
+    constexpr int LINES = (K * 4 + 127) / 128;     // 128-byte lines per output column
+    static_assert(LPV % U == 0, "U must divide LPV");
+    __shared__ int4 meta[WPB][2][LPV];
+
+    const int lane = threadIdx.x & (LPV - 1);
+    const int w = threadIdx.x / LPV;
+    const unsigned mask = worker_mask<LPV>();
+    const int c = blockIdx.x * WPB + w;
+    if (c >= nchunks) return;
+
+    const int4 dc = __ldg(desc + c);
+    const long long j0 = dc.x, j1 = dc.y;
+    const int nb = (int)((j1 - j0 + LPV - 1) / LPV);
+    const float *Dl = D + lane * 4;
+
+    auto stage = [&](int buf, long long base) {
+        const long long jj = base + lane;
+        int4 *dst = &meta[w][buf][lane];
+        if (jj < j1) {
+            cp_async4(&dst->x, gidx + jj);
+            cp_async4(&dst->y, val + jj);
+            cp_async4(&dst->z, seg + jj);
+        } else {
+            *dst = make_int4(__ldg(gidx + j1 - 1), 0, __ldg(seg + j1 - 1), 0);
+        }
+        cp_async_commit();
+    };
+
+    int cur = __ldg(seg + j0);
+    bool head_open = dc.z >= 0;
+    float4 acc[NT];
+    float4 oldv[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) { acc[t] = make_float4(0.f, 0.f, 0.f, 0.f); oldv[t] = acc[t]; }
+
+    auto prefetch_out = [&]() {
+        if (((unsigned)cur & storebit) == 0u) {
+            const float4 *o = reinterpret_cast<const float4 *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
+#pragma unroll
+            for (int t = 0; t < NT; t++) oldv[t] = o[t * LPV];
+        }
+    };
+
+    auto flush = [&](bool tail_open) {
+        if (!head_open && !tail_open) {
+            float4 *o = reinterpret_cast<float4 *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
+            if (((unsigned)cur & storebit) != 0u) {
+#pragma unroll
+                for (int t = 0; t < NT; t++) o[t * LPV] = acc[t];
+            } else {
+#pragma unroll
+                for (int t = 0; t < NT; t++) {
+                    float4 old = oldv[t];
+                    old.x += acc[t].x; old.y += acc[t].y; old.z += acc[t].z; old.w += acc[t].w;
+                    o[t * LPV] = old;
+                }
+            }
+        } else {
+            float4 *p = reinterpret_cast<float4 *>(part + (size_t)(head_open ? dc.z : dc.w) * K) + lane;
+#pragma unroll
+            for (int t = 0; t < NT; t++) p[t * LPV] = acc[t];
+        }
+    };
+
+    stage(0, j0);
+    if (PREFETCH) {
+        // output columns of the runs that start in the first batch (the one entering
+        // from the left, if any, goes to a slot and needs none)
+        const bool v0 = j0 + lane < j1;
+        const int s0 = v0 ? __ldg(seg + j0 + lane) : 0;
+        int p0 = __shfl_up_sync(mask, s0, 1, LPV);
+        if (lane == 0) p0 = head_open ? s0 : ~s0;
+        if (v0 && s0 != p0 && ((unsigned)s0 & storebit) == 0u) {
+            const char *o = reinterpret_cast<const char *>(O + (size_t)((unsigned)s0 & segmask) * K);
+#pragma unroll
+            for (int i = 0; i < LINES; i++) prefetch_l2(o + i * 128);
+        }
+    }
+    if (!head_open) prefetch_out();
+    for (int b = 0; b < nb; b++) {
+        int nseg = 0;
+        bool nvalid = false;
+        if (b + 1 < nb) {
+            const long long nbase = j0 + (long long)(b + 1) * LPV;
+            stage((b + 1) & 1, nbase);
+            if (PREFETCH) {
+                nvalid = nbase + lane < j1;
+                nseg = nvalid ? __ldg(seg + nbase + lane) : 0;     // consumed half a batch later
+            }
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        worker_sync<LPV>(mask);
+        const int4 *mt = meta[w][b & 1];
+
+        float4 x[2][U][NT];
+        int4 e[2][U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            e[0][u] = mt[u];
+            const float4 *d = reinterpret_cast<const float4 *>(Dl + (size_t)e[0][u].x * K);
+#pragma unroll
+            for (int t = 0; t < NT; t++) x[0][u][t] = __ldg(d + t * LPV);
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            if (g + 1 < G) {
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    e[(g + 1) & 1][u] = mt[(g + 1) * U + u];
+                    const float4 *d = reinterpret_cast<const float4 *>(Dl + (size_t)e[(g + 1) & 1][u].x * K);
+#pragma unroll
+                    for (int t = 0; t < NT; t++) x[(g + 1) & 1][u][t] = __ldg(d + t * LPV);
+                }
+            }
+            if (PREFETCH && g == G / 2) {
+                // output columns of the runs that start in the next batch, into L2
+                int pseg = __shfl_up_sync(mask, nseg, 1, LPV);
+                if (lane == 0) pseg = mt[LPV - 1].z;
+                if (nvalid && nseg != pseg && ((unsigned)nseg & storebit) == 0u) {
+                    const char *o = reinterpret_cast<const char *>(O + (size_t)((unsigned)nseg & segmask) * K);
+#pragma unroll
+                    for (int i = 0; i < LINES; i++) prefetch_l2(o + i * 128);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int4 m = e[g & 1][u];
+                if (m.z != cur) {
+                    flush(false);
+                    cur = m.z;
+                    head_open = false;
+                    prefetch_out();
+#pragma unroll
+                    for (int t = 0; t < NT; t++) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                const float v = __int_as_float(m.y);
+#pragma unroll
+                for (int t = 0; t < NT; t++) {
+                    const float4 xv = x[g & 1][u][t];
+                    acc[t].x = fmaf(v, xv.x, acc[t].x); acc[t].y = fmaf(v, xv.y, acc[t].y);
+                    acc[t].z = fmaf(v, xv.z, acc[t].z); acc[t].w = fmaf(v, xv.w, acc[t].w);
+                }
+            }
+        }
+        worker_sync<LPV>(mask);
+    }
+    flush(dc.w != -1);
+}
+
+// ---------------------------------------------------------------------------
+// Fix-up of a plan: one worker per split run {segment value, first slot, number
+// of pieces}.  The pieces lie in consecutive slots in chunk order; they are added
+// in that order and the total is added to (or, with the store bit, written over)
+// the output column.  No float atomics.
+// ---------------------------------------------------------------------------
+template <typename S, int VEC, int LPV, int NT>
+__global__ void __launch_bounds__(kThreads)
+plan_fixup_kernel(int k, int nruns, const int4 *__restrict__ runs, S *__restrict__ O,
+                  const S *__restrict__ part, unsigned segmask, unsigned storebit) {
+    typedef Vec<S, VEC> V;
+    typedef typename V::T VT;
+    const int lane = threadIdx.x & (LPV - 1);
+    const int r = (int)(((long long)blockIdx.x * kThreads + threadIdx.x) / LPV);
+    if (r >= nruns) return;
+    const int4 run = __ldg(runs + r);
+    const int ktile = blockIdx.y * (LPV * NT * VEC);
+    int eoff[NT];
+    bool eok[NT];
+    VT tot[NT], old[NT];
+    S *o = O + (size_t)((unsigned)run.x & segmask) * k;
+    const bool overwrite = ((unsigned)run.x & storebit) != 0u;
+    const S *p = part + (size_t)run.y * k;
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+        eoff[t] = ktile + (lane + t * LPV) * VEC;
+        eok[t] = eoff[t] < k;
+        tot[t] = eok[t] ? V::ld(p + eoff[t]) : V::zero();
+        old[t] = (eok[t] && !overwrite) ? V::ld(o + eoff[t]) : V::zero();
+    }
+    constexpr int PF = 4;
+    for (int q0 = 1; q0 < run.z; q0 += PF) {
+        VT x[PF][NT];
+#pragma unroll
+        for (int q = 0; q < PF; q++) {
+            const int qq = (q0 + q < run.z) ? q0 + q : run.z - 1;
+            const S *pq = p + (size_t)qq * k;
+#pragma unroll
+            for (int t = 0; t < NT; t++) x[q][t] = eok[t] ? V::ld(pq + eoff[t]) : V::zero();
+        }
+#pragma unroll
+        for (int q = 0; q < PF; q++)
+            if (q0 + q < run.z) {
+#pragma unroll
+                for (int t = 0; t < NT; t++) V::add(tot[t], x[q][t]);
+            }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; t++)
+        if (eok[t]) {
+            V::add(old[t], tot[t]);
+            V::st(o + eoff[t], old[t]);
+        }
+}
+
+}  // namespace bidmat

@@ -1,7 +1,6 @@
 // Stable LSD radix sort of the nonzero list by (column block, row), carrying
 // (column, value) as payload: the CSC -> row-major reordering that makes the
-// transposed product B*^S an atomic-free gather.  Included by one translation
-// unit only.
+// transposed product B*^S an atomic-free gather.
 //
 // key(j) = ((ic[j] >> colshift) << rowbits) | ir[j]      (unsigned 32 bit)
 //
@@ -36,7 +35,9 @@ __device__ __forceinline__ unsigned make_sort_key(int row, int col, SortKeySpec 
     return (((unsigned)col >> ks.colshift) << ks.rowbits) | (unsigned)row;
 }
 
-// FIRST: keys are computed from (ir, ic); otherwise read from keys_in.
+// FIRST: keys are computed from (ir, ic); otherwise read from keys_in.  In the first
+// scatter pass a null value array makes the position of each nonzero its payload,
+// which gives the permutation the sort applies.
 template <bool FIRST>
 __global__ void __launch_bounds__(kSortThreads)
 sort_hist_kernel(long long n, int ntiles, int shift, SortKeySpec ks, const unsigned *__restrict__ keys_in,
@@ -75,7 +76,7 @@ sort_hist_kernel(long long n, int ntiles, int shift, SortKeySpec ks, const unsig
 // and writes the segment total to seg_tot[d][seg].
 constexpr int kSortScanSegs = 32;
 
-__global__ void __launch_bounds__(kSortThreads)
+static __global__ void __launch_bounds__(kSortThreads)
 sort_scan_kernel(int ntiles, int tps, int *__restrict__ counts, int *__restrict__ seg_tot) {
     __shared__ int warp_sums[kSortWarps];
     __shared__ int carry_s;
@@ -111,7 +112,7 @@ sort_scan_kernel(int ntiles, int tps, int *__restrict__ counts, int *__restrict_
 
 // Level 2 (one CTA, thread = digit): turns seg_tot[d][seg] into the output
 // offset of the first key of digit d in segment seg.
-__global__ void __launch_bounds__(256) sort_digit_base_kernel(int *__restrict__ seg_tot) {
+static __global__ void __launch_bounds__(256) sort_digit_base_kernel(int *__restrict__ seg_tot) {
     __shared__ int s[256];
     const int d = threadIdx.x;
     int run = 0;
@@ -170,7 +171,7 @@ sort_scatter_kernel(long long n, int ntiles, int shift, SortKeySpec ks, const un
         if (ok) {
             const long long j = tile_base + pos;
             pa[r] = __ldg(a_in + j);
-            pb[r] = __ldg(b_in + j);
+            pb[r] = b_in ? __ldg(b_in + j) : (PV)j;      // no payload given: the position itself
             key[r] = FIRST ? make_sort_key(__ldg(ir + j), pa[r], ks) : __ldg(keys_in + j);
         }
     }
@@ -245,7 +246,7 @@ sort_scatter_kernel(long long n, int ntiles, int shift, SortKeySpec ks, const un
 }
 
 // largest row index: block reduction + integer atomicMax
-__global__ void __launch_bounds__(256) max_int_kernel(long long n, const int *__restrict__ v, int *__restrict__ out) {
+static __global__ void __launch_bounds__(256) max_int_kernel(long long n, const int *__restrict__ v, int *__restrict__ out) {
     int m = -2147483647 - 1;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const int x = __ldg(v + i);
@@ -260,7 +261,7 @@ __global__ void __launch_bounds__(256) max_int_kernel(long long n, const int *__
 }
 
 // off[b] = first sorted position whose key has column block >= b, b in [0, nblocks]
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 block_offsets_kernel(long long n, int nblocks, int rowbits, const unsigned *__restrict__ keys, int *__restrict__ off) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b > nblocks) return;

@@ -37,6 +37,29 @@ def _check(err, what):
         raise RuntimeError("%s %s" % (what, _lib.error_string(err)))
 
 
+def _stream(device):
+    """The stream the mirror's native calls run on: torch's current stream of the
+    operand's device, the one the tensors handed in were produced on.  BIDMat's
+    launchers use the per-thread default stream and synchronise it
+    (jni/include/MatKernel.hpp:15, jni/src/Arith.cu:57); here the stream-ordered entry
+    points run on torch's stream, which is then synchronised, so a call is complete on
+    return as in BIDMat and is ordered after whatever prepared its operands, also
+    inside `with torch.cuda.stream(s)`."""
+    return torch.cuda.current_stream(device)
+
+
+def _settle(device):
+    """Before a native call that runs on the per-thread default stream (the synchronous
+    entry points without a stream argument): wait for torch's current stream, on which the
+    operands were prepared, so the two streams cannot race."""
+    torch.cuda.current_stream(device).synchronize()
+
+
+def _finish(err, what, st):
+    _check(err, what)
+    st.synchronize()
+
+
 class SMat:
     """CPU sparse matrix in CSC form: jc (ncols+1), ir (nnz), data (nnz)."""
 
@@ -84,6 +107,74 @@ class SMat:
         S = S.tocsc()
         S.sort_indices()
         return SMat(S.shape[0], S.shape[1], S.indptr, S.indices, S.data)
+
+
+class TransposedPlan:
+    """Handle of a prepared transposed product (bidmat_b200_dsmultT_plan_create): the
+    row-sorted structure of one GSMat for dense operands of `k` rows.  BIDMat keeps
+    derived structure on the matrix object in the same way (pic, GSMat.scala:620-647)."""
+
+    OVERWRITE = 1
+    _INFO = ("nnz", "ncols", "m", "k", "elem_bytes", "blocks", "chunks", "split_runs", "slots", "cleared_rows",
+             "touched_rows", "bytes")
+
+    def __init__(self, k, S=None, elem_bytes=4, stream=None, m=None, ncols=None, pir=None, pic=None):
+        """From a GSMat `S`, or from raw device tensors pir / pic of an m x ncols structure."""
+        import ctypes
+        if S is not None:
+            m, ncols, pir, pic = S.nrows, S.ncols, S.pir, S.pic
+        self.handle = ctypes.c_void_p(0)
+        self.k, self.ncols, self.nnz, self.m = int(k), int(ncols), int(pir.numel()), int(m)
+        self.device = pir.device
+        with torch.cuda.device(self.device):
+            st = (stream or torch.cuda.current_stream()).cuda_stream
+            err = _L.bidmat_b200_dsmultT_plan_create(self.k, self.ncols, self.nnz, self.m, _ptr(pir), _ptr(pic),
+                                                     elem_bytes, st, ctypes.byref(self.handle))
+        _check(err, "CUMAT.dsmultT plan:")
+
+    def info(self):
+        import ctypes
+        out = (ctypes.c_longlong * len(self._INFO))()
+        _check(_L.bidmat_b200_plan_info(self.handle, out, len(self._INFO)), "plan_info")
+        return dict(zip(self._INFO, [int(v) for v in out]))
+
+    def touched_rows(self):
+        """Bitmap (int32 words, bit r%32 of word r//32) of the rows of S that hold a nonzero."""
+        out = torch.empty((self.m + 31) // 32, dtype=torch.int32, device=self.device)
+        with torch.cuda.device(self.device):
+            _check(_L.bidmat_b200_plan_touched_rows(self.handle, out.data_ptr(),
+                                                    torch.cuda.current_stream().cuda_stream), "plan_touched_rows")
+        return out
+
+    def verify(self, S):
+        """True when S still has the structure the plan was made from (exact check)."""
+        with torch.cuda.device(self.device):
+            err = _L.bidmat_b200_plan_verify(self.handle, S.ncols, S.nnz, _ptr(S.pir), _ptr(S.pic),
+                                             torch.cuda.current_stream().cuda_stream)
+        if err == 1:
+            return False
+        _check(err, "plan_verify")
+        return True
+
+    def run(self, B, S, out, flags=0, stream=None):
+        """out (k x m) += B (k x ncols) * S^T with S's current values (stream-ordered)."""
+        with torch.cuda.device(self.device):
+            st = (stream or torch.cuda.current_stream()).cuda_stream
+            err = _L.bidmat_b200_dsmultT_planned(self.handle, B.nrows, S.ncols, S.nnz, B.pdata, _ptr(S.pdata),
+                                                 out.pdata, flags, st)
+        _check(err, "GMult: CUDA kernel error in CUMAT.dsmultT (planned)")
+        return out
+
+    def close(self):
+        if self.handle:
+            _L.bidmat_b200_plan_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class GMat:
@@ -145,9 +236,11 @@ class GMat:
                                % (self.nrows, self.ncols, a.nrows, a.ncols, out.nrows, out.ncols))
         Mat.nflops += 2 * self.nrows * a.nnz
         a._debug_check()
-        err = _L.bidmat_b200_dsmult(self.nrows, a.ncols, a.nnz, self.pdata, _ptr(a.pdata),
-                                    _ptr(a.pir), _ptr(a.pic), out.pdata)
-        _check(err, "GMult: CUDA kernel error in CUMAT.dsmult")
+        with torch.cuda.device(self.t.device):
+            st = _stream(self.t.device)
+            err = _L.bidmat_b200_dsmult_async(self.nrows, a.ncols, a.nnz, self.pdata, _ptr(a.pdata),
+                                              _ptr(a.pir), _ptr(a.pic), out.pdata, st.cuda_stream)
+            _finish(err, "GMult: CUDA kernel error in CUMAT.dsmult", st)
         return out
 
     # ---- B *^ S ---------------------------------------------------------
@@ -169,9 +262,17 @@ class GMat:
                                % (self.nrows, self.ncols, a.ncols, a.nrows, out.nrows, out.ncols))
         Mat.nflops += 2 * self.nrows * a.nnz
         a._debug_check()
-        err = _L.bidmat_b200_dsmultT(self.nrows, a.ncols, a.nnz, self.pdata, _ptr(a.pdata),
-                                     _ptr(a.pir), _ptr(a.pic), out.pdata)
-        _check(err, "GMult: CUDA kernel error in CUMAT.dsmultT")
+        with torch.cuda.device(self.t.device):
+            st = _stream(self.t.device)
+            plan = a.transposed_plan(self.nrows, create=False)
+            if plan is not None:
+                # prepared structure: no sort, no host round trip (the values may be new)
+                err = _L.bidmat_b200_dsmultT_planned(plan.handle, self.nrows, a.ncols, a.nnz, self.pdata,
+                                                     _ptr(a.pdata), out.pdata, 0, st.cuda_stream)
+            else:
+                err = _L.bidmat_b200_dsmultT_async(self.nrows, a.ncols, a.nnz, self.pdata, _ptr(a.pdata),
+                                                   _ptr(a.pir), _ptr(a.pic), out.pdata, a.nrows, st.cuda_stream)
+            _finish(err, "GMult: CUDA kernel error in CUMAT.dsmultT", st)
         return out
 
     # ---- tiles (GMat.scala:961-997) --------------------------------------
@@ -184,6 +285,7 @@ class GMat:
                 or croff + nr > c.nrows or ccoff + nc > c.ncols):
             raise RuntimeError("%s: tile strays outside matrix dimensions" % name)
         Mat.nflops += 2 * nr * b.nnz
+        _settle(self.t.device)
         err = _L.bidmat_b200_dsmultTile(nr, nc, kk, b.nnz, self.pdata + 4 * (aroff + acoff * self.nrows), self.nrows,
                                         _ptr(b.pdata), _ptr(b.pir), _ptr(b.pic), broff, bcoff,
                                         c.pdata + 4 * (croff + ccoff * c.nrows), c.nrows, 1 if transpose else 0)
@@ -251,10 +353,34 @@ class GSMat:
         self.ncols = int(ncols)
         self.nnz = int(nnz)
         self.pir, self.pic, self.pjc, self.pdata = pir, pic, pjc, pdata
+        self._plans = {}     # dense height k -> TransposedPlan; shared with matrices that copy this pattern
 
     @property
     def device(self):
         return self.pjc.device
+
+    def transposed_plan(self, k, create=True):
+        """The prepared structure for `B *^ this` with dense operands of k rows.  Created on
+        request (prepareT) and kept on the matrix, like the per-nonzero columns BIDMat derives
+        once in fromSMat (GSMat.scala:620-647); DDS results share it because they copy this
+        matrix's pattern (GSMat.scala:656-661).  Changing pir/pic afterwards makes it stale:
+        call dropPlans().  With Mat.debugStructure every use is verified exactly."""
+        plan = self._plans.get(int(k))
+        if plan is None and create and self.nnz > 0:
+            plan = TransposedPlan(k, self)
+            self._plans[int(k)] = plan
+        if plan is not None and Mat.debugStructure and not plan.verify(self):
+            raise RuntimeError("GSMat: the prepared transposed structure does not match pir/pic")
+        return plan
+
+    def prepareT(self, k):
+        self.transposed_plan(k, create=True)
+        return self
+
+    def dropPlans(self):
+        for plan in self._plans.values():
+            plan.close()
+        self._plans = {}
 
     @staticmethod
     def of(a, device=None):
@@ -317,6 +443,7 @@ class GSMat:
         nn = n if n > 0 else (2 if self.nrows == 1 else 1)
         out = GMat.zeros(1 if nn == 1 else self.nrows, self.ncols if nn == 1 else 1, self.device)
         Mat.nflops += self.nnz
+        _settle(self.device)
         err = _L.bidmat_b200_spsum(self.nrows, self.ncols, self.nnz, _ptr(self.pir), _ptr(self.pic), _ptr(self.pdata),
                                    out.pdata, nn)
         _check(err, "Cuda error in GSMAT.sum")
@@ -332,6 +459,7 @@ class GSMat:
             raise RuntimeError("GSMat op GMat: dimensions mismatch")
         Mat.nflops += self.nnz
         out = self.copy()
+        _settle(self.device)
         if b.ncols > 1:
             err = _L.bidmat_b200_sdoprow(self.nrows, self.ncols, self.nnz, _ptr(out.pdata), _ptr(out.pic), b.pdata,
                                          length, op)
@@ -365,6 +493,7 @@ class GSMat:
 
     def _debug_check(self):
         if Mat.debugStructure and self.nnz:
+            _settle(self.device)
             err = _L.bidmat_b200_check_structure(self.nrows, self.ncols, self.nnz, _ptr(self.pir), _ptr(self.pic))
             _check(err, "GSMat structure check failed:")
 
@@ -386,10 +515,14 @@ class GSMat:
         out = C._like(oldmat)
         out.pir.copy_(C.pir)
         out.pic.copy_(C.pic)
+        out._plans = C._plans            # same pattern: the prepared structure carries over
         out.pdata.zero_()
         C._debug_check()
-        err = _L.bidmat_b200_dds(A.nrows, C.nnz, A.pdata, B.pdata, _ptr(C.pir), _ptr(C.pic), _ptr(out.pdata))
-        _check(err, "DDS kernel error")
+        with torch.cuda.device(C.device):
+            st = _stream(C.device)
+            err = _L.bidmat_b200_dds_async(A.nrows, C.nnz, A.pdata, B.pdata, _ptr(C.pir), _ptr(C.pic),
+                                           _ptr(out.pdata), st.cuda_stream)
+            _finish(err, "DDS kernel error", st)
         Mat.nflops += 2 * C.nnz * A.nrows
         return out
 
@@ -402,8 +535,11 @@ class GSMat:
         out.pir.copy_(C.pir)
         out.pic.copy_(C.pic)
         out.pdata.zero_()
-        err = _L.bidmat_b200_dds0(A.nrows, C.ncols, A.pdata, B.pdata, _ptr(C.pir), _ptr(C.pjc), _ptr(out.pdata))
-        _check(err, "DDS kernel error")
+        with torch.cuda.device(C.device):
+            st = _stream(C.device)
+            err = _L.bidmat_b200_dds0_async(A.nrows, C.ncols, C.nnz, A.pdata, B.pdata, _ptr(C.pir), _ptr(C.pjc),
+                                            _ptr(out.pdata), st.cuda_stream)
+            _finish(err, "DDS kernel error", st)
         Mat.nflops += 2 * C.nnz * A.nrows
         return out
 

@@ -106,12 +106,7 @@ def main():
             elif args.config == 5:
                 # P = DDS(A,B,S); C = A*S; G = B *^ P (P's values on S's pattern); allreduce G
                 def g_of_p():
-                    saved = shard.data
-                    shard.data = st.P
-                    try:
-                        st.dsmultT()
-                    finally:
-                        shard.data = saved
+                    st.dsmultT(data=st.P)     # P has S's pattern: the plan of S serves it
                 ops = [("DDS", st.dds), ("A*S", st.dsmult), ("B*^P", g_of_p)]
             else:
                 ops = [("A*S", st.dsmult), ("DDS", st.dds), ("B*^S", st.dsmultT)]

@@ -55,14 +55,30 @@ def make_shard(problem, rank, world):
 
 class PathStep:
     """A*S, DDS(A,B,S) and B*^S (+ allreduce) on one rank's shard, enqueued on
-    one stream through the stream-ordered C ABI."""
+    one stream through the stream-ordered C ABI.
 
-    def __init__(self, k, shard, A, B_local, stream, group=None, peer_reduce=False):
+    B*^S goes through a prepared plan of the shard's structure (sorted once, here
+    in the constructor) unless use_plan is False.  With a plan the product is
+    written in overwrite mode: the rows of G that the shard names are overwritten
+    every step and the others are never written, so G is not cleared between steps.
+      * one GPU: G starts as zeros, its untouched rows stay zero;
+      * several GPUs, peer-memory sum: every rank knows every rank's touched rows
+        (bitmaps exchanged once) and reads a peer's row only when that peer wrote
+        it, so what the untouched rows hold does not matter;
+      * several GPUs, NCCL: NCCL adds whole buffers, so G is cleared every step.
+    """
+
+    def __init__(self, k, shard, A, B_local, stream, group=None, peer_reduce=False, use_plan=True):
         self.k, self.S, self.A, self.B, self.stream, self.group = int(k), shard, A, B_local, stream, group
         dev = A.device
         self.C = torch.zeros((shard.n, k), dtype=torch.float32, device=dev)
         self.P = torch.zeros(shard.nnz, dtype=torch.float32, device=dev)
         self.peer = None
+        self.plan = None
+        self.touched = None
+        if use_plan and shard.nnz:
+            from .mat import TransposedPlan
+            self.plan = TransposedPlan(k, m=shard.m, ncols=shard.n, pir=shard.ir, pic=shard.ic)
         if group is not None and peer_reduce:
             # G lives in memory that the other GPUs of the box can address over NVLink;
             # the sum over ranks is then this library's own kernel, not a library collective.
@@ -77,6 +93,8 @@ class PathStep:
                 self.peer = None
         if self.peer is None:
             self.G = torch.zeros((shard.m, k), dtype=torch.float32, device=dev)
+        # clear G every step?  Not when the plan overwrites and nobody reads the untouched rows.
+        self.overwrite = self.plan is not None and (group is None or (self.peer is not None and self.touched is not None))
 
     def _setup_peer_memory(self, shard, k, dev, group):
         import ctypes
@@ -96,25 +114,50 @@ class PathStep:
             "ctas": int(os.environ.get("BIDMAT_B200_PEER_CTAS", "0")),
         }
         self.G.zero_()
+        if self.plan is not None and k % 4 == 0 and not int(os.environ.get("BIDMAT_B200_PEER_DENSE", "0")):
+            # every rank's touched-row bitmap, rank 0 first: exchanged once, the structure does not change
+            mine = self.plan.touched_rows()
+            allmaps = torch.empty(world * mine.numel(), dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(allmaps, mine, group=group)
+            self.touched = allmaps
+        torch.cuda.synchronize(dev)
+
+    def touched_fraction(self):
+        """Share of the m rows of G that this rank's shard names (None without a plan)."""
+        if self.plan is None:
+            return None
+        return self.plan.info()["touched_rows"] / float(max(1, self.S.m))
 
     def dsmult(self):
         S = self.S
-        self.C.zero_()   # GMat.GSMult clears the output before the native call (GMat.scala:1047)
-        _ck(_L.bidmat_b200_dsmult_async(self.k, S.n, S.nnz, self.A.data_ptr(), S.data.data_ptr(), S.ir.data_ptr(),
-                                        S.ic.data_ptr(), self.C.data_ptr(), self.stream.cuda_stream), "dsmult")
+        with torch.cuda.stream(self.stream):
+            self.C.zero_()   # GMat.GSMult clears the output before the native call (GMat.scala:1047)
+            _ck(_L.bidmat_b200_dsmult_async(self.k, S.n, S.nnz, self.A.data_ptr(), S.data.data_ptr(), S.ir.data_ptr(),
+                                            S.ic.data_ptr(), self.C.data_ptr(), self.stream.cuda_stream), "dsmult")
 
     def dds(self):
         S = self.S
-        self.P.zero_()   # GSMat.DDS clears the values first (GSMat.scala:662)
-        _ck(_L.bidmat_b200_dds_async(self.k, S.nnz, self.A.data_ptr(), self.B.data_ptr(), S.ir.data_ptr(),
-                                     S.ic.data_ptr(), self.P.data_ptr(), self.stream.cuda_stream), "dds")
+        with torch.cuda.stream(self.stream):
+            self.P.zero_()   # GSMat.DDS clears the values first (GSMat.scala:662)
+            _ck(_L.bidmat_b200_dds_async(self.k, S.nnz, self.A.data_ptr(), self.B.data_ptr(), S.ir.data_ptr(),
+                                         S.ic.data_ptr(), self.P.data_ptr(), self.stream.cuda_stream), "dds")
 
-    def dsmultT_local(self):
-        """This rank's partial of B*^S over its column shard (no communication)."""
+    def dsmultT_local(self, data=None):
+        """This rank's partial of B*^S over its column shard (no communication).
+        `data`: other values on the same structure (e.g. a DDS result), default S's own."""
         S = self.S
-        self.G.zero_()   # GMat.GSMultT clears the output (GMat.scala:1082)
-        _ck(_L.bidmat_b200_dsmultT_async(self.k, S.n, S.nnz, self.B.data_ptr(), S.data.data_ptr(), S.ir.data_ptr(),
-                                         S.ic.data_ptr(), self.G.data_ptr(), S.m, self.stream.cuda_stream), "dsmultT")
+        vals = S.data if data is None else data
+        with torch.cuda.stream(self.stream):
+            if not self.overwrite:
+                self.G.zero_()   # GMat.GSMultT clears the output (GMat.scala:1082)
+            if self.plan is not None:
+                _ck(_L.bidmat_b200_dsmultT_planned(self.plan.handle, self.k, S.n, S.nnz, self.B.data_ptr(),
+                                                   vals.data_ptr(), self.G.data_ptr(),
+                                                   1 if self.overwrite else 0, self.stream.cuda_stream), "dsmultT (planned)")
+            else:
+                _ck(_L.bidmat_b200_dsmultT_async(self.k, S.n, S.nnz, self.B.data_ptr(), vals.data_ptr(),
+                                                 S.ir.data_ptr(), S.ic.data_ptr(), self.G.data_ptr(), S.m,
+                                                 self.stream.cuda_stream), "dsmultT")
 
     def allreduce_start(self):
         """Starts the sum of the partials over ranks off the caller's stream, which
@@ -122,25 +165,34 @@ class PathStep:
         if self.group is None:
             return None
         import torch.distributed as dist
-        if self.peer is None:
-            return dist.all_reduce(self.G, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
-        pr = self.peer
-        # Rank synchronisation is a one-element NCCL allreduce before and after (it completes
-        # on a rank only when every rank has reached it in stream order); the data moves in
-        # this library's kernel over peer loads and stores.
-        before = dist.all_reduce(pr["flag"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
-        with torch.cuda.stream(pr["comm"]):
-            before.wait()
-            _ck(_L.bidmat_b200_peer_allreduce_sum(pr["world"], pr["rank"], pr["addrs"], self.G.numel(), pr["ctas"],
-                                                  pr["comm"].cuda_stream), "peer_allreduce_sum")
-            after = dist.all_reduce(pr["flag"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
-        return after
+        with torch.cuda.stream(self.stream):
+            if self.peer is None:
+                return dist.all_reduce(self.G, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            pr = self.peer
+            # Rank synchronisation is a one-element NCCL allreduce before and after (it completes
+            # on a rank only when every rank has reached it in stream order); the data moves in
+            # this library's kernel over peer loads and stores.
+            before = dist.all_reduce(pr["flag"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            with torch.cuda.stream(pr["comm"]):
+                before.wait()
+                if self.touched is not None:
+                    _ck(_L.bidmat_b200_peer_allreduce_sum_rows(pr["world"], pr["rank"], pr["addrs"], self.k, self.S.m,
+                                                               self.touched.data_ptr(), pr["ctas"],
+                                                               pr["comm"].cuda_stream), "peer_allreduce_sum_rows")
+                else:
+                    _ck(_L.bidmat_b200_peer_allreduce_sum(pr["world"], pr["rank"], pr["addrs"], self.G.numel(),
+                                                          pr["ctas"], pr["comm"].cuda_stream), "peer_allreduce_sum")
+                after = dist.all_reduce(pr["flag"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            return after
 
-    def dsmultT(self):
-        self.dsmultT_local()
-        work = self.allreduce_start()
+    def wait(self, work):
         if work is not None:
-            work.wait()
+            with torch.cuda.stream(self.stream):
+                work.wait()
+
+    def dsmultT(self, data=None):
+        self.dsmultT_local(data)
+        self.wait(self.allreduce_start())
 
     def run(self):
         """One pass of the path.  The three operations are independent, so the
@@ -150,5 +202,9 @@ class PathStep:
         work = self.allreduce_start()
         self.dsmult()
         self.dds()
-        if work is not None:
-            work.wait()
+        self.wait(work)
+
+    def close(self):
+        if self.plan is not None:
+            self.plan.close()
+            self.plan = None

@@ -23,9 +23,9 @@
  * The four functions without suffix are synchronous on the per-thread default
  * stream, exactly like the launchers they replace.  The *_async variants
  * enqueue on a caller-supplied stream and return without synchronising.
- * Scratch memory, where an operation needs it, comes from a per-device
- * workspace owned by the library (grown on demand, reused across calls,
- * released by bidmat_b200_release_workspace).
+ * Scratch memory, where an operation needs it, is allocated stream-ordered from a
+ * per-device pool owned by the library and returned before the call ends (see
+ * bidmat_b200_release_workspace / bidmat_b200_set_workspace_limit).
  */
 #ifndef BIDMAT_B200_H
 #define BIDMAT_B200_H
@@ -127,6 +127,55 @@ BIDMAT_B200_API int bidmat_b200_dds_f64_async(int nrows, int nnz, const double *
                                               const int *Cir, const int *Cic, double *P,
                                               bidmat_stream_t stream);
 
+/* Prepared transposed product.  bidmat_b200_dsmultT has to sort the nonzeros by row on
+ * every call, because the reference interface hands it nothing but raw arrays.  A caller
+ * that multiplies with the same sparse STRUCTURE again and again (any values) can prepare
+ * it once:
+ *   plan_create  sorts (Bir, Bic) of an m x ncols matrix for dense operands of `nrows`
+ *                rows of elem_bytes (4 or 8) each and keeps the sorted list, the source
+ *                position of every nonzero and the chunk layout on the device
+ *                (about 12 bytes per nonzero, freed by plan_destroy).  Synchronous.
+ *   planned      C(nrows x m) += A(nrows x ncols) * S^T with S = (Bir, Bic, Bdata): only
+ *                the values are read through the stored positions; no sort, no host round
+ *                trip, stream-ordered.  nrows, ncols and nnz must be those of the plan
+ *                (cudaErrorInvalidValue otherwise).  With BIDMAT_B200_PLAN_OVERWRITE the
+ *                columns of C named by at least one nonzero are overwritten with the
+ *                product instead of added to, and all other columns are left untouched
+ *                (plan_touched_rows tells which): a caller that would clear C first saves
+ *                the clearing and one read of C.
+ *   plan_verify  exact check that (Bir, Bic) is the structure the plan was made from
+ *                (0 = yes, cudaErrorInvalidValue = no).  Synchronous.
+ * A plan belongs to the device it was created on and may be used by one call at a time
+ * (calls on one stream, or ordered by the caller).  The result is bit-reproducible and
+ * uses no float atomics; terms of one output column are added in ascending source column
+ * inside a column block, blocks in ascending order, pieces of rows split over chunks last.
+ * No counterpart in the reference's native interface; the precedent is structure derived
+ * once and kept on the matrix object (GSMat.fromSMat computing pic,
+ * src/main/scala/BIDMat/GSMat.scala:620-647; DDS copying its argument's pattern,
+ * GSMat.scala:656-661).  Replaces the per-call work of dsmultT (jni/src/Arith.cu:234-248). */
+typedef struct bidmat_b200_plan *bidmat_b200_plan_t;
+#define BIDMAT_B200_PLAN_OVERWRITE 1
+BIDMAT_B200_API int bidmat_b200_dsmultT_plan_create(int nrows, int ncols, int nnz, int m, const int *Bir,
+                                                    const int *Bic, int elem_bytes, bidmat_stream_t stream,
+                                                    bidmat_b200_plan_t *plan);
+BIDMAT_B200_API int bidmat_b200_dsmultT_planned(bidmat_b200_plan_t plan, int nrows, int ncols, int nnz,
+                                                const float *A, const float *Bdata, float *C, int flags,
+                                                bidmat_stream_t stream);
+BIDMAT_B200_API int bidmat_b200_dsmultT_planned_f64(bidmat_b200_plan_t plan, int nrows, int ncols, int nnz,
+                                                    const double *A, const double *Bdata, double *C, int flags,
+                                                    bidmat_stream_t stream);
+BIDMAT_B200_API int bidmat_b200_plan_verify(bidmat_b200_plan_t plan, int ncols, int nnz, const int *Bir,
+                                            const int *Bic, bidmat_stream_t stream);
+/* out[0..count): nnz, ncols, m, nrows, elem_bytes, column blocks, chunks, split runs, slots,
+ * rows cleared by an overwriting call, rows named by at least one nonzero, device bytes held. */
+#define BIDMAT_B200_PLAN_INFO_COUNT 12
+BIDMAT_B200_API int bidmat_b200_plan_info(bidmat_b200_plan_t plan, long long *out, int count);
+/* Copies to the device array `bitmap` (ceil(m/32) words, caller-owned) which rows of S hold a
+ * nonzero: bit r%32 of word r/32 is set for such a row r.  Stream-ordered. */
+BIDMAT_B200_API int bidmat_b200_plan_touched_rows(bidmat_b200_plan_t plan, unsigned *bitmap,
+                                                  bidmat_stream_t stream);
+BIDMAT_B200_API int bidmat_b200_plan_destroy(bidmat_b200_plan_t plan);
+
 /* A*S without any allocation.  No counterpart in the reference: BIDMat's
  * launchers never needed scratch memory.  It exists for callers that cannot let a
  * library allocate on the device: host applications that have handed all device
@@ -170,6 +219,19 @@ BIDMAT_B200_API int bidmat_b200_dsmult_noalloc(int nrows, int ncols, int nnz, co
  *   (src/main/scala/BIDMat/GFunctions.scala:175-203, jni/src/BIDMat_NCCL.cpp:80-90). */
 BIDMAT_B200_API int bidmat_b200_peer_allreduce_sum(int world, int rank, const unsigned long long *peer_addresses,
                                                    long long count, int ctas, bidmat_stream_t stream);
+
+/* The same sum for a k x m result (k % 4 == 0) when it is known which of its m columns
+ * ("rows" of the sparse matrix) every rank wrote: touched is a device array of
+ * world * ceil(m/32) words, rank r's bitmap first to last (bidmat_b200_plan_touched_rows of
+ * each rank's plan, gathered once).  A rank's column is read only when that rank wrote it,
+ * so no rank has to clear its buffer between steps (columns it did not write may hold the
+ * previous sum) and less crosses NVLink; columns nobody wrote are set to zero.  Together
+ * with BIDMAT_B200_PLAN_OVERWRITE this removes the clearing of the k x m partial from the
+ * step.  Same ordering rules as bidmat_b200_peer_allreduce_sum. */
+BIDMAT_B200_API int bidmat_b200_peer_allreduce_sum_rows(int world, int rank,
+                                                        const unsigned long long *peer_addresses, int k,
+                                                        long long m, const unsigned *touched, int ctas,
+                                                        bidmat_stream_t stream);
 
 /* Structure helpers on the device (the steps BIDMat performs around the path
  * with cuSPARSE csr2coo and a host loop: GSMat.fromSMat, GSMat.scala:639, and
@@ -232,10 +294,18 @@ BIDMAT_B200_API int bidmat_b200_spsum(int nrows, int ncols, int nnz, const int *
  * Synchronous. */
 BIDMAT_B200_API int bidmat_b200_check_structure(int m, int ncols, int nnz, const int *ir, const int *ic);
 
-/* Bytes currently held by the calling thread's device workspace, and its
- * release (frees the device memory; the next call grows it again). */
+/* Scratch memory.  Every call that needs scratch takes it from a memory pool the library
+ * owns on the calling thread's device, by stream-ordered allocation on the call's stream,
+ * and gives it back on that stream before returning; freed blocks stay cached in the pool
+ * for the next call.  workspace_bytes: bytes the pool currently holds.  release_workspace:
+ * hands everything that is not in use back to the driver.  set_workspace_limit: the largest
+ * scratch request (bytes, 0 = unlimited) a single call may make on this device; a call that
+ * needs more returns cudaErrorMemoryAllocation before launching anything and leaves the
+ * device and the library usable (a host whose own allocator owns the device memory can
+ * bound what this library takes). */
 BIDMAT_B200_API long long bidmat_b200_workspace_bytes(void);
 BIDMAT_B200_API int bidmat_b200_release_workspace(void);
+BIDMAT_B200_API int bidmat_b200_set_workspace_limit(long long bytes);
 
 /* Number of kernels this library has launched in this process (all devices);
  * the benchmark reports the difference across its timed region. */

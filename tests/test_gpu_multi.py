@@ -30,7 +30,9 @@ def _worker(rank, world, port, q):
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from datetime import timedelta
+    # a lone rank gives up instead of waiting inside a collective for a peer that died
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=timedelta(seconds=120))
     try:
         from bidmat_b200 import gen, step as pstep
         p = gen.config2(0.03, seed=5, device=dev)
@@ -46,7 +48,7 @@ def _worker(rank, world, port, q):
                 torch.cuda.synchronize()
                 dist.barrier()
                 outs[mode] = st.G.clone()
-        same_bits = torch.equal(outs[False].view(torch.int32), outs[True].view(torch.int32))
+        same_bits = torch.equal(outs[False], outs[True])      # two ranks: a + b in either implementation
         other = outs[True].clone()
         dist.broadcast(other, src=0)
         same_across_ranks = torch.equal(other.view(torch.int32), outs[True].view(torch.int32))
@@ -58,7 +60,9 @@ def _worker(rank, world, port, q):
             want = oracle.dsmultT(Bh, data, ir, jc, p.m)
             _, scale = oracle.dsmultT_f64(Bh, data, ir, jc, p.m)
             ok = bool(np.all(np.abs(outs[True].cpu().numpy().astype(np.float64) - want) <= RTOL_DSMULTT * scale + 1e-30))
-            q.put((same_bits, same_across_ranks, ok))
+            q.put((rank, same_bits, same_across_ranks, ok))
+        else:
+            q.put((rank, same_bits, same_across_ranks, True))
     finally:
         dist.destroy_process_group()
 
@@ -73,10 +77,21 @@ def test_peer_memory_sum_matches_nccl_on_two_gpus():
     procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(500)
-        assert p.exitcode == 0
-    same_bits, same_across_ranks, ok = q.get(timeout=10)
-    assert same_bits, "peer-memory sum and NCCL allreduce differ for two ranks"
-    assert same_across_ranks, "ranks ended with different G"
-    assert ok, "sharded B*^S differs from the CPU checker"
+    try:
+        results = {}
+        for _ in procs:
+            r = q.get(timeout=500)            # every rank reports: a missing report is a failure
+            results[r[0]] = r[1:]
+        for p in procs:
+            p.join(60)
+    finally:
+        for p in procs:                       # never leave a child spinning on the device
+            if p.is_alive():
+                p.kill()
+                p.join()
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert sorted(results) == [0, 1]
+    for rank, (same_bits, same_across_ranks, ok) in results.items():
+        assert same_bits, "rank %d: peer-memory sum and NCCL allreduce differ for two ranks" % rank
+        assert same_across_ranks, "rank %d: ranks ended with different G" % rank
+        assert ok, "sharded B*^S differs from the CPU checker"
