@@ -55,6 +55,9 @@ _SIGNATURES = {
     "bidmat_b200_sdoprow": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _c_int, _c_int]),
     "bidmat_b200_sdopcol": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _c_int, _c_int]),
     "bidmat_b200_spsum": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _c_int]),
+    "bidmat_b200_spsum_f64": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _c_int]),
+    "bidmat_b200_sdoprow_f64": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _c_int, _c_int]),
+    "bidmat_b200_sdopcol_f64": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _c_int, _c_int]),
     "bidmat_b200_check_structure": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp]),
     "bidmat_b200_workspace_bytes": (ctypes.c_longlong, []),
     "bidmat_b200_release_workspace": (_c_int, []),

@@ -15,6 +15,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIBDIR = os.path.join(PKG, "lib")
 LIBNAME = "libbidmatcuda_b200.so"
 LIBPATH = os.path.join(LIBDIR, LIBNAME)
+COMPAT_OBJ = os.path.join(LIBDIR, "matkernel_compat.o")
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
@@ -35,6 +36,14 @@ def find_jni_include():
         inc = os.path.join(r, "include")
         if os.path.exists(os.path.join(inc, "jni.h")):
             return [inc, os.path.join(inc, "linux")]
+    return None
+
+
+def find_nccl():
+    """(include dir, library dir) of an NCCL 2 installation, or None."""
+    for inc, lib in (("/usr/include", "/usr/lib/x86_64-linux-gnu"), ("/usr/local/cuda/include", "/usr/local/cuda/lib64")):
+        if os.path.exists(os.path.join(inc, "nccl.h")) and glob.glob(os.path.join(lib, "libnccl.so*")):
+            return inc, lib
     return None
 
 
@@ -66,8 +75,18 @@ def build(force=False, verbose=False):
             cmd += ["-I", d]
         cmd += ["-DBIDMAT_B200_WITH_JNI=1"]
         srcs.append(os.path.join(CSRC, "jni_shim.cpp"))
+        nccl = find_nccl()
+        if nccl:      # the edu.berkeley.bid.NCCL natives on NCCL 2
+            cmd += ["-I", nccl[0], "-L", nccl[1], "-lnccl", "-DBIDMAT_B200_WITH_NCCL=1"]
+            srcs.append(os.path.join(CSRC, "nccl_jni_shim.cpp"))
     cmd += srcs
     subprocess.check_call(cmd)
+    # MatKernel.hpp launcher names on top of the C ABI, for linking into BIDMat's own
+    # libbidmatcuda (kept out of this library: see the file's header)
+    cxx = shutil.which("g++")
+    if cxx:
+        subprocess.check_call([cxx, "-std=c++17", "-O2", "-c", "-fPIC", "-I", os.path.join(PKG, "..", "include"),
+                               os.path.join(CSRC, "matkernel_compat.cpp"), "-o", COMPAT_OBJ])
     return LIBPATH
 
 

@@ -149,6 +149,73 @@ int dds0_impl(int nrows, int ncols, int nnz, const S *A, const S *B,
     return (int)launch_dds<S, false>(nrows, nnz, A, B, Cir, ic, P, st);
 }
 
+template <typename S>
+int sdop_common(int nnz, S *A, const int *idx, const S *B, int len, int opn) {
+    if (nnz < 0 || len < 0 || opn < 0 || opn >= kNumBinops) return (int)cudaErrorInvalidValue;
+    if (nnz == 0) return 0;
+    if (!A || !B || (len > 1 && !idx)) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = cudaStreamPerThread;
+    size_t blocks = ((size_t)nnz + kThreads - 1) / kThreads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    sdop_kernel<S><<<(unsigned)blocks, kThreads, 0, st>>>(nnz, A, len > 1 ? idx : nullptr, B, opn);
+    g_launches += 1;
+    return finish_sync(cudaGetLastError(), st);
+}
+
+// B[seg[j]] += P[j] for a non-decreasing seg: segmented sum, then the fix-up of the runs
+// that cross chunk boundaries (the gather-accumulate fix-up with one element per column).
+template <typename S>
+cudaError_t launch_segsum(long long nnz, const S *P, const int *seg, S *B, S *part, cudaStream_t st) {
+    constexpr int ITEMS = 16;
+    constexpr int CHUNK = 32 * ITEMS;
+    const long long nchunks = (nnz + CHUNK - 1) / CHUNK;
+    {
+        ScopedSpan sp("spsum_segsum", st);
+        segsum_chunk_kernel<S, ITEMS><<<blocks_for(nchunks, 32), kThreads, 0, st>>>(nnz, nchunks, P, seg, B, part);
+    }
+    if (nchunks > 1)
+        ga_fixup_kernel<S, 1, 8, 1><<<blocks_for(nchunks, 8), kThreads, 0, st>>>(1, nnz, CHUNK, nchunks, seg, B, part,
+                                                                                 nullptr, 0xffffffffu, 1);
+    g_launches += (nchunks > 1) ? 2 : 1;
+    return cudaGetLastError();
+}
+
+template <typename S>
+int spsum_impl(int nrows, int ncols, int nnz, const int *Air, const int *Aic, const S *P, S *B, int n) {
+    if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (nnz == 0) return 0;
+    if (!Air || !Aic || !P || !B) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = cudaStreamPerThread;
+    const size_t n_ = (size_t)nnz;
+    const size_t part_elems = 2 * ((n_ + 511) / 512) + 2;
+    if (n == 1) {
+        // B(1 x ncols)[ic[j]] += P[j]: the column indices are already sorted
+        WorkspaceLease ws(pad256(part_elems * sizeof(S)) + 256, st);
+        if (ws.err != cudaSuccess) return (int)ws.err;
+        S *part = ws.take<S>(part_elems);
+        return finish_sync(launch_segsum<S>(nnz, P, Aic, B, part, st), st);
+    }
+    // B(nrows x 1)[ir[j]] += P[j]: stable sort of (row, value) by row first, then the same kernel
+    const int ntiles = (int)((n_ + kSortTile - 1) / kSortTile);
+    int rowbits = ceil_log2((unsigned long long)(nrows > 0 ? nrows : 1));
+    if (rowbits < 1) rowbits = 1;
+    if (rowbits > 31) return (int)cudaErrorInvalidValue;
+    WorkspaceLease ws(4 * pad256(n_ * 4) + 2 * pad256(n_ * sizeof(S)) + pad256((size_t)256 * ntiles * 4) +
+                          pad256(256 * kSortScanSegs * 4) + pad256(part_elems * sizeof(S)) + 4096, st);
+    if (ws.err != cudaSuccess) return (int)ws.err;
+    unsigned *keys[2] = {ws.take<unsigned>(n_), ws.take<unsigned>(n_)};
+    int *cols[2] = {ws.take<int>(n_), ws.take<int>(n_)};
+    S *vals[2] = {ws.take<S>(n_), ws.take<S>(n_)};
+    int *counts = ws.take<int>((size_t)256 * ntiles);
+    int *totals = ws.take<int>(256 * kSortScanSegs);
+    S *part = ws.take<S>(part_elems);
+    const int cur = run_rowsort<S>(nnz, (rowbits + 7) / 8, SortKeySpec{31, rowbits}, Air, Aic, P, keys, cols, vals,
+                                   nullptr, nullptr, nullptr, counts, totals, st);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return (int)err;
+    return finish_sync(launch_segsum<S>(nnz, vals[cur], reinterpret_cast<const int *>(keys[cur]), B, part, st), st);
+}
+
 }  // namespace
 
 extern "C" {
@@ -343,79 +410,33 @@ int bidmat_b200_check_structure(int m, int ncols, int nnz, const int *ir, const 
     return h ? (int)cudaErrorInvalidValue : 0;
 }
 
-static int sdop_common(int nnz, float *A, const int *idx, const float *B, int len, int opn) {
-    if (nnz < 0 || len < 0 || opn < 0 || opn >= kNumBinops) return (int)cudaErrorInvalidValue;
-    if (nnz == 0) return 0;
-    if (!A || !B || (len > 1 && !idx)) return (int)cudaErrorInvalidValue;
-    cudaStream_t st = cudaStreamPerThread;
-    size_t blocks = ((size_t)nnz + kThreads - 1) / kThreads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
-    sdop_kernel<<<(unsigned)blocks, kThreads, 0, st>>>(nnz, A, len > 1 ? idx : nullptr, B, opn);
-    g_launches += 1;
-    return finish_sync(cudaGetLastError(), st);
-}
-
 int bidmat_b200_sdoprow(int nrows, int ncols, int nnz, float *A, const int *Aic, const float *B, int len, int opn) {
     (void)nrows; (void)ncols;
-    return sdop_common(nnz, A, Aic, B, len, opn);
+    return sdop_common<float>(nnz, A, Aic, B, len, opn);
 }
 
 int bidmat_b200_sdopcol(int nrows, int ncols, int nnz, float *A, const int *Air, const float *B, int len, int opn) {
     (void)nrows; (void)ncols;
-    return sdop_common(nnz, A, Air, B, len, opn);
+    return sdop_common<float>(nnz, A, Air, B, len, opn);
+}
+
+int bidmat_b200_sdoprow_f64(int nrows, int ncols, int nnz, double *A, const int *Aic, const double *B, int len, int opn) {
+    (void)nrows; (void)ncols;
+    return sdop_common<double>(nnz, A, Aic, B, len, opn);
+}
+
+int bidmat_b200_sdopcol_f64(int nrows, int ncols, int nnz, double *A, const int *Air, const double *B, int len, int opn) {
+    (void)nrows; (void)ncols;
+    return sdop_common<double>(nnz, A, Air, B, len, opn);
 }
 
 int bidmat_b200_spsum(int nrows, int ncols, int nnz, const int *Air, const int *Aic, const float *P, float *B, int n) {
-    if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
-    if (nnz == 0) return 0;
-    if (!Air || !Aic || !P || !B) return (int)cudaErrorInvalidValue;
-    cudaStream_t st = cudaStreamPerThread;
-    // Both sums are the gather-accumulate kernel with a 1 x 1 dense operand holding
-    // 1.0: B[seg[j]] += P[j] * 1, summed without atomics in nonzero order.
-    const Shape s = pick_shape(1, false);
-    const int chunk = pick_chunk(nnz, s.lpv);
-    const size_t n_ = (size_t)nnz;
-    if (n == 1) {
-        // B(1 x ncols)[ic[j]] += P[j]: the column indices are already sorted
-        WorkspaceLease ws(pad256(n_ * 4) + pad256(ga_part_floats(1, nnz, chunk) * 4) + 1024, st);
-        if (ws.err != cudaSuccess) return (int)ws.err;
-        int *zeros = ws.take<int>(n_);
-        float *part = ws.take<float>(ga_part_floats(1, nnz, chunk));
-        float *one = ws.take<float>(1);
-        cudaError_t err = cudaMemsetAsync(zeros, 0, n_ * 4, st);
-        if (err != cudaSuccess) return (int)err;
-        fill_one_kernel<<<1, 1, 0, st>>>(one);
-        g_launches += 1;
-        err = launch_ga<float>(1, nnz, one, P, zeros, Aic, B, part, chunk, s, st, "spsum_ga_chunk");
-        return finish_sync(err, st);
-    }
-    // B(nrows x 1)[ir[j]] += P[j]: stable sort by row first, then the same kernel
-    const int ntiles = (int)((n_ + kSortTile - 1) / kSortTile);
-    int rowbits = ceil_log2((unsigned long long)(nrows > 0 ? nrows : 1));
-    if (rowbits < 1) rowbits = 1;
-    if (rowbits > 31) return (int)cudaErrorInvalidValue;
-    WorkspaceLease ws(7 * pad256(n_ * 4) + pad256((size_t)256 * ntiles * 4) + pad256(256 * kSortScanSegs * 4) +
-                          pad256(ga_part_floats(1, nnz, chunk) * 4) + 4096, st);
-    if (ws.err != cudaSuccess) return (int)ws.err;
-    unsigned *keys[2] = {ws.take<unsigned>(n_), ws.take<unsigned>(n_)};
-    int *cols[2] = {ws.take<int>(n_), ws.take<int>(n_)};
-    float *vals[2] = {ws.take<float>(n_), ws.take<float>(n_)};
-    int *zeros = ws.take<int>(n_);
-    int *counts = ws.take<int>((size_t)256 * ntiles);
-    int *totals = ws.take<int>(256 * kSortScanSegs);
-    float *part = ws.take<float>(ga_part_floats(1, nnz, chunk));
-    float *one = ws.take<float>(1);
-    cudaError_t err = cudaMemsetAsync(zeros, 0, n_ * 4, st);
-    if (err != cudaSuccess) return (int)err;
-    fill_one_kernel<<<1, 1, 0, st>>>(one);
-    g_launches += 1;
-    const int cur = run_rowsort<float>(nnz, (rowbits + 7) / 8, SortKeySpec{31, rowbits}, Air, Aic, P, keys, cols, vals,
-                                       nullptr, nullptr, nullptr, counts, totals, st);
-    err = cudaGetLastError();
-    if (err != cudaSuccess) return (int)err;
-    err = launch_ga<float>(1, nnz, one, vals[cur], zeros, reinterpret_cast<const int *>(keys[cur]), B, part, chunk, s,
-                           st, "spsum_ga_chunk");
-    return finish_sync(err, st);
+    return spsum_impl<float>(nrows, ncols, nnz, Air, Aic, P, B, n);
+}
+
+int bidmat_b200_spsum_f64(int nrows, int ncols, int nnz, const int *Air, const int *Aic, const double *P, double *B,
+                          int n) {
+    return spsum_impl<double>(nrows, ncols, nnz, Air, Aic, P, B, n);
 }
 
 // C(nr x nc tile) += A(nr x kk tile) * S[broff:broff+kk, bcoff:bcoff+nc]       (transpose == 0)

@@ -110,8 +110,8 @@ JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_spsum(JNIEnv *env, jclass, ji
                              (float *)device_address(env, jB), n);
 }
 
-// Rebinding these two also captures BIDMat's double-precision overloads of the same
-// Java methods; only bind them when GSDMat edge operators are not in use.
+// Edge operators: sdoprow / sdopcol are the fp32 natives; the double-precision ones are
+// separate natives, sdopdrow / sdopdcol (CUMAT.java:137,141), bound below.
 JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_sdoprow(JNIEnv *env, jclass, jint nrows, jint ncols, jint nnz,
                                                           jobject jA, jobject jAic, jobject jB, jint len, jint opn) {
     if (!init_field_ids(env)) return 1;
@@ -126,7 +126,31 @@ JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_sdopcol(JNIEnv *env, jclass, 
                                (const int *)device_address(env, jAir), (const float *)device_address(env, jB), len, opn);
 }
 
-// Double-precision natives of edu.berkeley.bid.CUMATD (CUMATD.java:51,57,89,91).
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_sdopdrow(JNIEnv *env, jclass, jint nrows, jint ncols, jint nnz,
+                                                           jobject jA, jobject jAic, jobject jB, jint len, jint opn) {
+    if (!init_field_ids(env)) return 1;
+    return bidmat_b200_sdoprow_f64(nrows, ncols, nnz, (double *)device_address(env, jA),
+                                   (const int *)device_address(env, jAic), (const double *)device_address(env, jB),
+                                   len, opn);
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMAT_sdopdcol(JNIEnv *env, jclass, jint nrows, jint ncols, jint nnz,
+                                                           jobject jA, jobject jAir, jobject jB, jint len, jint opn) {
+    if (!init_field_ids(env)) return 1;
+    return bidmat_b200_sdopcol_f64(nrows, ncols, nnz, (double *)device_address(env, jA),
+                                   (const int *)device_address(env, jAir), (const double *)device_address(env, jB),
+                                   len, opn);
+}
+
+JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMATD_spsum(JNIEnv *env, jclass, jint nrows, jint ncols, jint nnz,
+                                                         jobject jAir, jobject jAic, jobject jP, jobject jB, jint n) {
+    if (!init_field_ids(env)) return 1;
+    return bidmat_b200_spsum_f64(nrows, ncols, nnz, (const int *)device_address(env, jAir),
+                                 (const int *)device_address(env, jAic), (const double *)device_address(env, jP),
+                                 (double *)device_address(env, jB), n);
+}
+
+// Double-precision natives of edu.berkeley.bid.CUMATD (CUMATD.java:51,57,71,89,91).
 JNIEXPORT jint JNICALL Java_edu_berkeley_bid_CUMATD_dsmult(JNIEnv *env, jclass, jint nrows, jint ncols, jint nnz,
                                                           jobject jA, jobject jBdata, jobject jBir, jobject jBic,
                                                           jobject jC) {

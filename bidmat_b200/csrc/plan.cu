@@ -9,6 +9,7 @@
 // every G = B *^ DDS(A,B,S) of a factorisation loop.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <climits>
 #include <cstdint>
 #include <vector>
@@ -29,13 +30,14 @@ struct bidmat_b200_plan {
     int *cols = nullptr;           // source column per sorted nonzero
     int *perm = nullptr;           // original position per sorted nonzero
     int4 *desc = nullptr;          // chunk descriptors, all blocks
-    int4 *runs = nullptr;          // split runs {key, first slot, pieces, 0}
+    int4 *runs = nullptr;          // split runs {key, first slot, pieces, 0}, ordered by (row, block)
+    int4 *groups = nullptr;        // rows with split runs {row, first run, number of runs, 0}
     int *clear_rows = nullptr;     // rows cleared by an overwriting call (first run is split)
     unsigned *touched = nullptr;   // bitmap of the rows named by at least one nonzero
     void *part = nullptr;          // slots of the split runs, nslots * k elements
     int *mismatch = nullptr;       // result of plan_verify
     std::vector<int> block_c0, block_nch;
-    int nchunks = 0, nruns = 0, nslots = 0, nclear = 0;
+    int nchunks = 0, nruns = 0, ngroups = 0, nslots = 0, nclear = 0;
     long long touched_rows = 0;
     size_t bytes = 0;
 };
@@ -55,7 +57,7 @@ template <typename T> cudaError_t plan_alloc(bidmat_b200_plan *p, T **out, size_
 }
 
 void plan_free(bidmat_b200_plan *p) {
-    cudaFree(p->keys); cudaFree(p->cols); cudaFree(p->perm); cudaFree(p->desc); cudaFree(p->runs);
+    cudaFree(p->keys); cudaFree(p->cols); cudaFree(p->perm); cudaFree(p->desc); cudaFree(p->runs); cudaFree(p->groups);
     cudaFree(p->clear_rows); cudaFree(p->touched); cudaFree(p->part); cudaFree(p->mismatch);
     p->magic = 0;
     delete p;
@@ -198,11 +200,24 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
     }
     p->nslots = slot;
     p->nruns = (int)h_runs.size();
+    // Runs were listed block after block; a row split in several blocks has several.  Bring the
+    // runs of one row together, blocks ascending (stable sort by row), and list the rows.
+    std::stable_sort(h_runs.begin(), h_runs.end(), [&](const int4 &a, const int4 &b) {
+        return ((unsigned)a.x & lay.rowmask) < ((unsigned)b.x & lay.rowmask);
+    });
+    std::vector<int4> h_groups;
+    for (size_t r = 0; r < h_runs.size(); r++) {
+        const int row = (int)((unsigned)h_runs[r].x & lay.rowmask);
+        if (h_groups.empty() || h_groups.back().x != row) h_groups.push_back(make_int4(row, (int)r, 0, 0));
+        h_groups.back().z++;
+    }
+    p->ngroups = (int)h_groups.size();
     p->nclear = (int)h_clear.size();
     for (int r = 0; r < m; r++) p->touched_rows += (h_first[r] != kNoBlock);
 
     PLAN_CK(plan_alloc(p, &p->desc, (size_t)total));
     PLAN_CK(plan_alloc(p, &p->runs, h_runs.size()));
+    PLAN_CK(plan_alloc(p, &p->groups, h_groups.size()));
     PLAN_CK(plan_alloc(p, &p->clear_rows, h_clear.size()));
     PLAN_CK(plan_alloc(p, &p->touched, ((size_t)m + 31) / 32));
     {
@@ -213,6 +228,8 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
     PLAN_CK(cudaMemcpyAsync(p->desc, h_desc.data(), (size_t)total * sizeof(int4), cudaMemcpyHostToDevice, st));
     if (!h_runs.empty())
         PLAN_CK(cudaMemcpyAsync(p->runs, h_runs.data(), h_runs.size() * sizeof(int4), cudaMemcpyHostToDevice, st));
+    if (!h_groups.empty())
+        PLAN_CK(cudaMemcpyAsync(p->groups, h_groups.data(), h_groups.size() * sizeof(int4), cudaMemcpyHostToDevice, st));
     if (!h_clear.empty())
         PLAN_CK(cudaMemcpyAsync(p->clear_rows, h_clear.data(), h_clear.size() * sizeof(int), cudaMemcpyHostToDevice, st));
     {
@@ -311,11 +328,16 @@ int plan_run(bidmat_b200_plan *p, int k, int ncols, int nnz, const S *A, const S
     if (p->nruns > 0) {
         ScopedSpan sp("ga_fixup", st);
         dim3 grid(blocks_for(p->nruns, s.lpv), s.tiles, 1);
-#define CALL_FIX(VEC, LPV, NT) \
-    plan_fixup_kernel<S, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, p->nruns, p->runs, C, part, segmask, storebit)
+        dim3 ggrid(blocks_for(p->ngroups, s.lpv), s.tiles, 1);
+#define CALL_FIX(VEC, LPV, NT)                                                                              \
+    do {                                                                                                    \
+        plan_fixup_runs_kernel<S, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, p->nruns, p->runs, part);     \
+        plan_fixup_rows_kernel<S, VEC, LPV, NT><<<ggrid, kThreads, 0, st>>>(k, p->ngroups, p->groups, p->runs, C, \
+                                                                            part, segmask);                 \
+    } while (0)
         DISPATCH_SHAPE(s, CALL_FIX);
 #undef CALL_FIX
-        g_launches += 1;
+        g_launches += 2;
     }
     return (int)cudaGetLastError();
 }

@@ -51,9 +51,22 @@ plan_bounds_kernel(int lo, int hi, int T, int nch, const unsigned *__restrict__ 
 template <typename S>
 __global__ void __launch_bounds__(256)
 plan_permute_kernel(long long n, const int *__restrict__ perm, const S *__restrict__ data, S *__restrict__ vals) {
+    // four independent position -> value chains per thread and iteration: the gathers are
+    // 4- or 8-byte reads at scattered addresses, bound by the number of requests in flight
+    constexpr int UN = 4;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += stride)
-        vals[j] = __ldg(data + __ldg(perm + j));
+    long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; j + (UN - 1) * stride < n; j += UN * stride) {
+        int p[UN];
+        S v[UN];
+#pragma unroll
+        for (int u = 0; u < UN; u++) p[u] = __ldg(perm + j + u * stride);
+#pragma unroll
+        for (int u = 0; u < UN; u++) v[u] = __ldg(data + p[u]);
+#pragma unroll
+        for (int u = 0; u < UN; u++) vals[j + u * stride] = v[u];
+    }
+    for (; j < n; j += stride) vals[j] = __ldg(data + __ldg(perm + j));
 }
 
 // Exact check that (ir, ic) is the structure a plan was built from: every sorted
@@ -299,15 +312,19 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
 }
 
 // ---------------------------------------------------------------------------
-// Fix-up of a plan: one worker per split run {segment value, first slot, number
-// of pieces}.  The pieces lie in consecutive slots in chunk order; they are added
-// in that order and the total is added to (or, with the store bit, written over)
-// the output column.  No float atomics.
+// Fix-up of a plan, in two launches and without float atomics.
+//  1. plan_fixup_runs_kernel: one worker per split run {segment value, first slot,
+//     number of pieces}.  The pieces lie in consecutive slots in chunk order; they are
+//     added in that order and the total replaces the first piece.
+//  2. plan_fixup_rows_kernel: one worker per output column that has split runs
+//     {segment value, first run, number of runs}: a row of the sparse matrix can be
+//     split in several column blocks, so its run totals are added here, by one worker,
+//     in block order, and the sum is added to the output column once.  (Letting every
+//     run update the output itself would race between the runs of one row.)
 // ---------------------------------------------------------------------------
 template <typename S, int VEC, int LPV, int NT>
 __global__ void __launch_bounds__(kThreads)
-plan_fixup_kernel(int k, int nruns, const int4 *__restrict__ runs, S *__restrict__ O,
-                  const S *__restrict__ part, unsigned segmask, unsigned storebit) {
+plan_fixup_runs_kernel(int k, int nruns, const int4 *__restrict__ runs, S *__restrict__ part) {
     typedef Vec<S, VEC> V;
     typedef typename V::T VT;
     const int lane = threadIdx.x & (LPV - 1);
@@ -317,16 +334,13 @@ plan_fixup_kernel(int k, int nruns, const int4 *__restrict__ runs, S *__restrict
     const int ktile = blockIdx.y * (LPV * NT * VEC);
     int eoff[NT];
     bool eok[NT];
-    VT tot[NT], old[NT];
-    S *o = O + (size_t)((unsigned)run.x & segmask) * k;
-    const bool overwrite = ((unsigned)run.x & storebit) != 0u;
-    const S *p = part + (size_t)run.y * k;
+    VT tot[NT];
+    S *p = part + (size_t)run.y * k;
 #pragma unroll
     for (int t = 0; t < NT; t++) {
         eoff[t] = ktile + (lane + t * LPV) * VEC;
         eok[t] = eoff[t] < k;
         tot[t] = eok[t] ? V::ld(p + eoff[t]) : V::zero();
-        old[t] = (eok[t] && !overwrite) ? V::ld(o + eoff[t]) : V::zero();
     }
     constexpr int PF = 4;
     for (int q0 = 1; q0 < run.z; q0 += PF) {
@@ -344,6 +358,39 @@ plan_fixup_kernel(int k, int nruns, const int4 *__restrict__ runs, S *__restrict
 #pragma unroll
                 for (int t = 0; t < NT; t++) V::add(tot[t], x[q][t]);
             }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; t++)
+        if (eok[t]) V::st(p + eoff[t], tot[t]);
+}
+
+template <typename S, int VEC, int LPV, int NT>
+__global__ void __launch_bounds__(kThreads)
+plan_fixup_rows_kernel(int k, int ngroups, const int4 *__restrict__ groups, const int4 *__restrict__ runs,
+                       S *__restrict__ O, const S *__restrict__ part, unsigned segmask) {
+    typedef Vec<S, VEC> V;
+    typedef typename V::T VT;
+    const int lane = threadIdx.x & (LPV - 1);
+    const int g = (int)(((long long)blockIdx.x * kThreads + threadIdx.x) / LPV);
+    if (g >= ngroups) return;
+    const int4 grp = __ldg(groups + g);
+    const int ktile = blockIdx.y * (LPV * NT * VEC);
+    int eoff[NT];
+    bool eok[NT];
+    VT tot[NT], old[NT];
+    S *o = O + (size_t)((unsigned)grp.x & segmask) * k;
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+        eoff[t] = ktile + (lane + t * LPV) * VEC;
+        eok[t] = eoff[t] < k;
+        old[t] = eok[t] ? V::ld(o + eoff[t]) : V::zero();
+        tot[t] = V::zero();
+    }
+    for (int r = 0; r < grp.z; r++) {
+        const S *p = part + (size_t)__ldg(&runs[grp.y + r].y) * k;
+#pragma unroll
+        for (int t = 0; t < NT; t++)
+            if (eok[t]) { VT x = V::ld(p + eoff[t]); V::add(tot[t], x); }
     }
 #pragma unroll
     for (int t = 0; t < NT; t++)

@@ -278,6 +278,13 @@ BIDMAT_B200_API int bidmat_b200_sdoprow(int nrows, int ncols, int nnz, float *A,
                                         int len, int opn);
 BIDMAT_B200_API int bidmat_b200_sdopcol(int nrows, int ncols, int nnz, float *A, const int *Air, const float *B,
                                         int len, int opn);
+/* Double-precision edge operators: BIDMat binds them as separate natives, sdopdrow / sdopdcol
+ * (CUMAT.java:137,141, BIDMat_CUMAT.cpp:263-271, 284-293), onto the double overloads of
+ * sdoprow / sdopcol (jni/include/MatKernel.hpp:49,53). */
+BIDMAT_B200_API int bidmat_b200_sdoprow_f64(int nrows, int ncols, int nnz, double *A, const int *Aic,
+                                            const double *B, int len, int opn);
+BIDMAT_B200_API int bidmat_b200_sdopcol_f64(int nrows, int ncols, int nnz, double *A, const int *Air,
+                                            const double *B, int len, int opn);
 
 /* Sums of the values of a GSMat: n == 1: B(1 x ncols)[Aic[j]] += P[j] (column sums);
  * otherwise B(nrows x 1)[Air[j]] += P[j] (row sums).  Accumulates, without float
@@ -287,6 +294,9 @@ BIDMAT_B200_API int bidmat_b200_sdopcol(int nrows, int ncols, int nnz, float *A,
  *   CUMAT.java:209, BIDMat_CUMAT.cpp:873-881). */
 BIDMAT_B200_API int bidmat_b200_spsum(int nrows, int ncols, int nnz, const int *Air, const int *Aic,
                                       const float *P, float *B, int n);
+/* Double-precision twin (spsum on doubles, jni/include/MatKernelD.hpp:51, CUMATD.java:71). */
+BIDMAT_B200_API int bidmat_b200_spsum_f64(int nrows, int ncols, int nnz, const int *Air, const int *Aic,
+                                          const double *P, double *B, int n);
 
 /* Validates a GSMat structure on the device without touching values:
  * 0 <= ir < m, 0 <= ic < ncols, ic non-decreasing.  Returns 0 when it holds,

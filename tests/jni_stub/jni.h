@@ -1,6 +1,6 @@
 /*
  * TEST INFRASTRUCTURE.  A stand-in for the JDK's <jni.h> with just the C++
- * declarations that bidmat_b200/csrc/jni_shim.cpp uses, so that the shim can be
+ * declarations that bidmat_b200/csrc/jni_shim.cpp and nccl_jni_shim.cpp use, so that the shims can be
  * compile-checked where no JDK is installed (tests/test_jni_shim.py).  It is
  * never used to build the product library.
  */
@@ -13,6 +13,8 @@ typedef int64_t jlong;
 class _jobject {};
 typedef _jobject *jobject;
 typedef jobject jclass;
+typedef jobject jobjectArray;
+typedef jint jsize;
 struct _jfieldID;
 typedef _jfieldID *jfieldID;
 
@@ -32,6 +34,9 @@ struct JNIEnv {
     jclass FindClass(const char *name);
     jfieldID GetFieldID(jclass clazz, const char *name, const char *sig);
     jlong GetLongField(jobject obj, jfieldID field);
+    void SetLongField(jobject obj, jfieldID field, jlong value);
+    jsize GetArrayLength(jobjectArray array);
+    jobject GetObjectArrayElement(jobjectArray array, jsize index);
     void ExceptionClear();
     jint RegisterNatives(jclass clazz, const JNINativeMethod *methods, jint count);
 };

@@ -68,6 +68,30 @@ def test_spsum_rows_and_columns(cuda_device, m, n, dens, monkeypatch):
         np.add.at(scale, idx, np.abs(P).astype(np.float64))
         assert np.all(np.abs(outs[0] - want) <= 1e-5 * scale + 1e-30)
         assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+        # double-precision twin (spsum on doubles, MatKernelD.hpp:51)
+        B64 = dev(start.astype(np.float64), cuda_device)
+        P64 = dev(P.astype(np.float64), cuda_device)
+        assert L.bidmat_b200_spsum_f64(m, n, S.nnz, S.ir.data_ptr(), S.ic.data_ptr(), P64.data_ptr(), B64.data_ptr(), nn) == 0
+        assert np.all(np.abs(B64.cpu().numpy() - want) <= 1e-13 * scale + 1e-30)
+
+
+@pytest.mark.parametrize("opn", [0, 2, 3, 10, 13])
+def test_double_precision_edge_operators(cuda_device, opn):
+    """sdopdrow / sdopdcol (CUMAT.java:137,141): the double overloads."""
+    from bidmat_b200 import _lib
+    L = _lib.lib
+    rng = np.random.default_rng(40 + opn)
+    m, n = 60, 45
+    jc, ir, data = random_csc(m, n, 0.25, rng)
+    S = DeviceCSC(m, n, jc, ir, data, cuda_device)
+    d64 = data.astype(np.float64) + 1e-9
+    row, col = rng.uniform(0.2, 2.0, n), rng.uniform(0.2, 2.0, m)
+    f = {0: np.add, 2: np.multiply, 3: np.divide, 10: np.maximum, 13: np.power}[opn]
+    for fn, idx_d, idx_h, vec in ((L.bidmat_b200_sdoprow_f64, S.ic, S.ic_h, row), (L.bidmat_b200_sdopcol_f64, S.ir, S.ir_h, col)):
+        A = dev(d64.copy(), cuda_device)
+        B = dev(vec, cuda_device)
+        assert fn(m, n, S.nnz, A.data_ptr(), idx_d.data_ptr(), B.data_ptr(), len(vec), opn) == 0
+        assert np.allclose(A.cpu().numpy(), f(d64, vec[idx_h]), rtol=(1e-15 if opn != 13 else 1e-14), atol=0)
 
 
 def test_mirror_sum_and_edge_operators(cuda_device):

@@ -108,8 +108,37 @@ def test_planned_product_with_split_runs_and_column_blocks(cuda_device, k, chunk
     assert info["slots"] >= 2 * info["split_runs"]
     if cols_per_block:
         assert info["blocks"] > 1
-    else:
+    elif chunk <= 32:
         assert info["split_runs"] > 0 and info["cleared_rows"] > 0
+
+
+@pytest.mark.parametrize("k", [64, 256])
+def test_rows_split_in_every_column_block(cuda_device, k, monkeypatch):
+    """A few long rows over many columns with small column blocks and chunks: every row is
+    split in every block, so one row has many split runs whose totals must be added by one
+    worker (a per-run update of the output would race).  Repeated to expose a race."""
+    monkeypatch.setenv("BIDMAT_B200_CHUNK", "8")
+    monkeypatch.setenv("BIDMAT_B200_COLBLOCK_COLS", "64")
+    rng = np.random.default_rng(k)
+    m, n = 6, 1500
+    jc, ir, data = random_csc(m, n, 0.85, rng)
+    S = DeviceCSC(m, n, jc, ir, data, cuda_device)
+    B = rng.standard_normal((n, k)).astype(np.float32)
+    dB = dev(B, cuda_device)
+    plan = Plan(k, S)
+    info = plan.info()
+    assert info["blocks"] >= 20 and info["split_runs"] >= 5 * info["blocks"]
+    want = oracle.dsmultT(B, data, ir, jc, m)
+    _, Gabs = oracle.dsmultT_f64(B, data, ir, jc, m)
+    first = None
+    for rep in range(20):
+        for flags in (0, OVERWRITE):
+            G = plan.run(dB, S, torch.zeros((m, k), device=cuda_device), flags)
+            assert_close_scaled(G.cpu().numpy(), want, Gabs, RTOL_DSMULTT, "split in every block, rep %d" % rep)
+            if first is None:
+                first = G.clone()
+            assert torch.equal(first.view(torch.int32), G.view(torch.int32))
+    plan.close()
 
 
 def test_planned_product_on_skewed_rows(cuda_device):
