@@ -29,6 +29,7 @@ struct bidmat_b200_plan {
     unsigned *keys = nullptr;      // sorted (column block << rowbits) | row, bit 31 = first block of the row
     int *cols = nullptr;           // source column per sorted nonzero
     int *perm = nullptr;           // original position per sorted nonzero
+    int *inv = nullptr;            // sorted position per original nonzero (BIDMAT_B200_PLAN_SCATTER=1 only)
     int4 *desc = nullptr;          // chunk descriptors, all blocks
     int4 *runs = nullptr;          // split runs {key, first slot, pieces, 0}, ordered by (row, block)
     int4 *groups = nullptr;        // rows with split runs {row, first run, number of runs, 0}
@@ -57,7 +58,7 @@ template <typename T> cudaError_t plan_alloc(bidmat_b200_plan *p, T **out, size_
 }
 
 void plan_free(bidmat_b200_plan *p) {
-    cudaFree(p->keys); cudaFree(p->cols); cudaFree(p->perm); cudaFree(p->desc); cudaFree(p->runs); cudaFree(p->groups);
+    cudaFree(p->keys); cudaFree(p->cols); cudaFree(p->perm); cudaFree(p->inv); cudaFree(p->desc); cudaFree(p->runs); cudaFree(p->groups);
     cudaFree(p->clear_rows); cudaFree(p->touched); cudaFree(p->part); cudaFree(p->mismatch);
     p->magic = 0;
     delete p;
@@ -126,6 +127,13 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
         PLAN_CK(cudaStreamSynchronize(st));
     }
 
+    if (env_int("BIDMAT_B200_PLAN_SCATTER", 0)) {
+        PLAN_CK(plan_alloc(p, &p->inv, n));
+        plan_invert_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(nnz, p->perm, p->inv);
+        g_launches += 1;
+        PLAN_CK(cudaGetLastError());
+    }
+
     // ---- chunk grid of every block
     std::vector<int> T((size_t)lay.nblocks, 0);
     p->block_c0.assign((size_t)lay.nblocks, 0);
@@ -135,7 +143,10 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
         const long long count = (long long)h_off[b + 1] - h_off[b];
         p->block_c0[b] = total;
         if (count <= 0) continue;
-        T[b] = pick_chunk(count, 1);       // boundaries move to row boundaries anyway: no rounding to the worker width
+        // half the chunk length of the unprepared path (twice the chunks per launch): measured 0.3 ms
+        // less over the 16 launches of the LDA configuration; boundaries move to row boundaries anyway,
+        // so no rounding to the worker width
+        T[b] = pick_chunk((count + 1) / 2, 1);
         p->block_nch[b] = (int)((count + T[b] - 1) / T[b]);
         total += p->block_nch[b];
     }
@@ -143,24 +154,27 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
     const size_t nb_entries = (size_t)total + (size_t)lay.nblocks;      // nch + 1 boundaries per block
     std::vector<int> h_start(nb_entries);
     std::vector<unsigned> h_kfirst(nb_entries), h_kprev(nb_entries);
+    std::vector<int> h_fcol(nb_entries);
     {
-        WorkspaceLease ws(3 * pad256(nb_entries * 4) + 1024, st);
+        WorkspaceLease ws(4 * pad256(nb_entries * 4) + 1024, st);
         PLAN_CK(ws.err);
         int *d_start = ws.take<int>(nb_entries);
         unsigned *d_first = ws.take<unsigned>(nb_entries);
         unsigned *d_prev = ws.take<unsigned>(nb_entries);
+        int *d_fcol = ws.take<int>(nb_entries);
         for (int b = 0; b < lay.nblocks; b++) {
             const int nch = p->block_nch[b];
             if (nch == 0) continue;
             const size_t e0 = (size_t)p->block_c0[b] + b;
-            plan_bounds_kernel<<<(nch + 256) / 256, 256, 0, st>>>(h_off[b], h_off[b + 1], T[b], nch, p->keys,
-                                                                  d_start + e0, d_first + e0, d_prev + e0);
+            plan_bounds_kernel<<<(nch + 256) / 256, 256, 0, st>>>(h_off[b], h_off[b + 1], T[b], nch, p->keys, p->cols,
+                                                                  d_start + e0, d_first + e0, d_prev + e0, d_fcol + e0);
             g_launches += 1;
         }
         PLAN_CK(cudaGetLastError());
         PLAN_CK(cudaMemcpyAsync(h_start.data(), d_start, nb_entries * 4, cudaMemcpyDeviceToHost, st));
         PLAN_CK(cudaMemcpyAsync(h_kfirst.data(), d_first, nb_entries * 4, cudaMemcpyDeviceToHost, st));
         PLAN_CK(cudaMemcpyAsync(h_kprev.data(), d_prev, nb_entries * 4, cudaMemcpyDeviceToHost, st));
+        PLAN_CK(cudaMemcpyAsync(h_fcol.data(), d_fcol, nb_entries * 4, cudaMemcpyDeviceToHost, st));
         PLAN_CK(cudaStreamSynchronize(st));
     }
 
@@ -196,6 +210,25 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
                 d.w = tail ? -2 : -1;
             }
             h_desc[(size_t)p->block_c0[b] + c] = d;
+        }
+        // Chunks that lie inside ONE long row (first key == last key, cut at both ends or at
+        // one) gather a contiguous range of source columns.  The workers of a CTA take
+        // consecutive descriptors, so such chunks are ordered by their first source column
+        // instead of by row: the workers of one CTA then walk the same columns of the dense
+        // operand for different rows at the same time and share them through L1.  Only the
+        // order of the descriptors changes; slots and runs stay attached to their chunks.
+        if (env_int("BIDMAT_B200_PLAN_COLORDER", 1)) {
+            std::vector<int> pos;
+            for (int c = 0; c < nch; c++) {
+                const size_t e = e0 + c;
+                const int4 &d = h_desc[(size_t)p->block_c0[b] + c];
+                if (h_kfirst[e] == h_kprev[e + 1] && (d.z >= 0 || d.w != -1)) pos.push_back(c);
+            }
+            std::vector<int> order(pos);
+            std::stable_sort(order.begin(), order.end(), [&](int a, int c2) { return h_fcol[e0 + a] < h_fcol[e0 + c2]; });
+            std::vector<int4> moved(pos.size());
+            for (size_t i = 0; i < pos.size(); i++) moved[i] = h_desc[(size_t)p->block_c0[b] + order[i]];
+            for (size_t i = 0; i < pos.size(); i++) h_desc[(size_t)p->block_c0[b] + pos[i]] = moved[i];
         }
     }
     p->nslots = slot;
@@ -267,12 +300,19 @@ int plan_run(bidmat_b200_plan *p, int k, int ncols, int nnz, const S *A, const S
     S *part = static_cast<S *>(p->part);
     const int *seg = reinterpret_cast<const int *>(p->keys);
 
-    WorkspaceLease ws(pad256(n * sizeof(S)) + 256, st);
+    // The predicate-free float kernel reads the values through the stored positions itself
+    // (BIDMAT_B200_PLAN_FUSED=0 switches that off); every other shape first brings them into
+    // the plan's order with one gather pass into scratch.
+    bool fast = false;
+    if constexpr (std::is_same<S, float>::value) fast = fast_shape(k, s) && !env_int("BIDMAT_B200_GENERIC", 0);
+    const bool fused = fast && env_int("BIDMAT_B200_PLAN_FUSED", 1) != 0;
+    WorkspaceLease ws(fused ? 256 : pad256(n * sizeof(S)) + 256, st);
     if (ws.err != cudaSuccess) return (int)ws.err;
-    S *vals = ws.take<S>(n);
-    {
+    S *vals = fused ? nullptr : ws.take<S>(n);
+    if (!fused) {
         ScopedSpan sp("dsmultT_permute", st);
-        plan_permute_kernel<S><<<148 * 16, 256, 0, st>>>((long long)nnz, p->perm, Bdata, vals);
+        if (p->inv) plan_scatter_kernel<S><<<148 * 16, 256, 0, st>>>((long long)nnz, p->inv, Bdata, vals);
+        else plan_permute_kernel<S><<<148 * 16, 256, 0, st>>>((long long)nnz, p->perm, Bdata, vals);
         g_launches += 1;
     }
     if (storebit && p->nclear > 0) {
@@ -288,17 +328,20 @@ int plan_run(bidmat_b200_plan *p, int k, int ncols, int nnz, const S *A, const S
         ScopedSpan sp("dsmultT_ga_chunk", st);
         bool done = false;
         if constexpr (std::is_same<S, float>::value) {
-            if (fast_shape(k, s) && !env_int("BIDMAT_B200_GENERIC", 0)) {
+            if (fast) {
                 const int wpb = kFastThreads / s.lpv;
                 const unsigned fgrid = (unsigned)((nch + wpb - 1) / wpb);
 #define CALL_PLAN(LPV, NT, U, MINB)                                                                             \
     do {                                                                                                        \
-        if (prefetch)                                                                                           \
-            ga_plan_fast_kernel<LPV, NT, U, kFastThreads, MINB, true><<<fgrid, kFastThreads, 0, st>>>(          \
-                nch, desc, A, vals, p->cols, seg, C, part, segmask, storebit);                                  \
+        if (fused)                                                                                              \
+            ga_plan_fast_kernel<LPV, NT, U, kFastThreads, MINB, true, true><<<fgrid, kFastThreads, 0, st>>>(    \
+                nch, desc, A, Bdata, p->perm, p->cols, seg, C, part, segmask, storebit);                        \
+        else if (prefetch)                                                                                      \
+            ga_plan_fast_kernel<LPV, NT, U, kFastThreads, MINB, true, false><<<fgrid, kFastThreads, 0, st>>>(   \
+                nch, desc, A, vals, nullptr, p->cols, seg, C, part, segmask, storebit);                         \
         else                                                                                                    \
-            ga_plan_fast_kernel<LPV, NT, U, kFastThreads, MINB, false><<<fgrid, kFastThreads, 0, st>>>(         \
-                nch, desc, A, vals, p->cols, seg, C, part, segmask, storebit);                                  \
+            ga_plan_fast_kernel<LPV, NT, U, kFastThreads, MINB, false, false><<<fgrid, kFastThreads, 0, st>>>(  \
+                nch, desc, A, vals, nullptr, p->cols, seg, C, part, segmask, storebit);                         \
     } while (0)
                 if (s.lpv == 8) CALL_PLAN(8, 1, 4, 0);
                 else if (s.lpv == 16) CALL_PLAN(16, 1, 4, 0);

@@ -19,12 +19,14 @@ namespace bidmat {
 // the run of equal keys that contains it, unless that run began at or before the
 // previous nominal boundary (then the run is longer than a chunk and is cut at
 // the nominal position).  Every chunk is non-empty and shorter than 2T.
-// Outputs, for c in [0, nch]: start[c], the key at start[c] (first[c]) and the key
-// just before it (prev[c]); c = nch describes the end of the block.
+// Outputs, for c in [0, nch]: start[c], the key at start[c] (first[c]), the key just
+// before it (prev[c]) and the source column at start[c] (fcol[c]); c = nch describes
+// the end of the block.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-plan_bounds_kernel(int lo, int hi, int T, int nch, const unsigned *__restrict__ keys,
-                   int *__restrict__ start, unsigned *__restrict__ first, unsigned *__restrict__ prev) {
+plan_bounds_kernel(int lo, int hi, int T, int nch, const unsigned *__restrict__ keys, const int *__restrict__ cols,
+                   int *__restrict__ start, unsigned *__restrict__ first, unsigned *__restrict__ prev,
+                   int *__restrict__ fcol) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c > nch) return;
     int b;
@@ -43,6 +45,7 @@ plan_bounds_kernel(int lo, int hi, int T, int nch, const unsigned *__restrict__ 
     start[c] = b;
     first[c] = (b < hi) ? __ldg(keys + b) : 0xffffffffu;
     prev[c] = (b > lo) ? __ldg(keys + b - 1) : 0xffffffffu;
+    fcol[c] = (b < hi) ? __ldg(cols + b) : 0x7fffffff;
 }
 
 // vals[j] = data[perm[j]]: the values of a call, brought into the plan's order.
@@ -67,6 +70,26 @@ plan_permute_kernel(long long n, const int *__restrict__ perm, const S *__restri
         for (int u = 0; u < UN; u++) vals[j + u * stride] = v[u];
     }
     for (; j < n; j += stride) vals[j] = __ldg(data + __ldg(perm + j));
+}
+
+// The same permutation written as a scatter: vals[inv[i]] = data[i] with coalesced reads.
+// Consecutive source positions are the nonzeros of one column in ascending row; the
+// nonzeros of a frequent row in neighbouring columns land next to each other in the
+// sorted list, so their 4-byte writes meet in the same L2 sectors shortly after one
+// another, where the gather form misses on every access.
+template <typename S>
+__global__ void __launch_bounds__(256)
+plan_scatter_kernel(long long n, const int *__restrict__ inv, const S *__restrict__ data, S *__restrict__ vals) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        vals[__ldg(inv + i)] = __ldg(data + i);
+}
+
+// inv[perm[j]] = j
+__global__ void __launch_bounds__(256)
+plan_invert_kernel(long long n, const int *__restrict__ perm, int *__restrict__ inv) {
+    const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < n) inv[__ldg(perm + j)] = (int)j;
 }
 
 // Exact check that (ir, ic) is the structure a plan was built from: every sorted
@@ -149,20 +172,26 @@ __device__ __forceinline__ void prefetch_l2(const void *p) {
 //     so the read of the output column would be a DRAM round trip per run on the
 //     critical path: while batch b is processed, the output columns of the runs
 //     that START in batch b+1 are prefetched into L2 (no registers held);
-//   * a run whose segment value has `storebit` set overwrites its output column.
+//   * a run whose segment value has `storebit` set overwrites its output column;
+//   * FUSED: `val` is the caller's value array in its own (CSC) order and `perm` the
+//     source position of every sorted nonzero.  The positions are staged two batches
+//     ahead and the values one batch ahead through them, so the scattered 4-byte reads
+//     (each a DRAM sector) overlap the gathers of this kernel, which leaves DRAM mostly
+//     idle, instead of costing a pass of their own (plan_permute_kernel).
 // ---------------------------------------------------------------------------
-template <int LPV, int NT, int U, int TPB, int MINB, bool PREFETCH>
+template <int LPV, int NT, int U, int TPB, int MINB, bool PREFETCH, bool FUSED>
 __global__ void __launch_bounds__(TPB, MINB)
 ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
-                    const float *__restrict__ D, const float *__restrict__ val,
+                    const float *__restrict__ D, const float *__restrict__ val, const int *__restrict__ perm,
                     const int *__restrict__ gidx, const int *__restrict__ seg,
                     float *__restrict__ O, float *__restrict__ part, unsigned segmask, unsigned storebit) {
     constexpr int K = 4 * LPV * NT;
     constexpr int WPB = TPB / LPV;
     constexpr int G = LPV / U;
     constexpr int LINES = (K * 4 + 127) / 128;     // 128-byte lines per output column
+    constexpr int NBUF = FUSED ? 3 : 2;            // staged batches of {index, value, segment, position}
     static_assert(LPV % U == 0, "U must divide LPV");
-    __shared__ int4 meta[WPB][2][LPV];
+    __shared__ int4 meta[WPB][NBUF][LPV];
 
     const int lane = threadIdx.x & (LPV - 1);
     const int w = threadIdx.x / LPV;
@@ -175,15 +204,29 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
     const int nb = (int)((j1 - j0 + LPV - 1) / LPV);
     const float *Dl = D + lane * 4;
 
-    auto stage = [&](int buf, long long base) {
-        const long long jj = base + lane;
-        int4 *dst = &meta[w][buf][lane];
-        if (jj < j1) {
-            cp_async4(&dst->x, gidx + jj);
-            cp_async4(&dst->y, val + jj);
-            cp_async4(&dst->z, seg + jj);
-        } else {
-            *dst = make_int4(__ldg(gidx + j1 - 1), 0, __ldg(seg + j1 - 1), 0);
+    // Every call commits exactly one cp.async group, also for a batch beyond the chunk
+    // (an empty group), so the wait counts below do not depend on where the chunk ends.
+    auto stage = [&](int batch) {                  // indices, segments and values or (FUSED) positions
+        if (batch < nb) {
+            const long long jj = j0 + (long long)batch * LPV + lane;
+            int4 *dst = &meta[w][batch % NBUF][lane];
+            if (jj < j1) {
+                cp_async4(&dst->x, gidx + jj);
+                cp_async4(&dst->z, seg + jj);
+                if (FUSED) cp_async4(&dst->w, perm + jj);
+                else cp_async4(&dst->y, val + jj);
+            } else {
+                // padding of the last batch: repeat the last nonzero with value 0
+                *dst = make_int4(__ldg(gidx + j1 - 1), 0, __ldg(seg + j1 - 1), -1);
+            }
+        }
+        cp_async_commit();
+    };
+    auto stage_values = [&](int batch) {           // FUSED: values through the positions staged before
+        if (batch < nb) {
+            const long long jj = j0 + (long long)batch * LPV + lane;
+            int4 *dst = &meta[w][batch % NBUF][lane];
+            if (jj < j1) cp_async4(&dst->y, val + dst->w);     // this lane's own position: visible after its wait
         }
         cp_async_commit();
     };
@@ -224,7 +267,12 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
         }
     };
 
-    stage(0, j0);
+    stage(0);
+    if (FUSED) {
+        stage(1);
+        cp_async_wait<1>();        // positions of batch 0 are in
+        stage_values(0);
+    }
     if (PREFETCH) {
         // output columns of the runs that start in the first batch (the one entering
         // from the left, if any, goes to a slot and needs none)
@@ -242,19 +290,23 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
     for (int b = 0; b < nb; b++) {
         int nseg = 0;
         bool nvalid = false;
-        if (b + 1 < nb) {
+        if (PREFETCH && b + 1 < nb) {
             const long long nbase = j0 + (long long)(b + 1) * LPV;
-            stage((b + 1) & 1, nbase);
-            if (PREFETCH) {
-                nvalid = nbase + lane < j1;
-                nseg = nvalid ? __ldg(seg + nbase + lane) : 0;     // consumed half a batch later
-            }
-            cp_async_wait<1>();
+            nvalid = nbase + lane < j1;
+            nseg = nvalid ? __ldg(seg + nbase + lane) : 0;         // consumed half a batch later
+        }
+        if (FUSED) {
+            // groups in commit order: ... P(b+1) V(b) | P(b+2) V(b+1)   (P positions+indices, V values)
+            stage(b + 2);
+            cp_async_wait<2>();        // all but V(b), P(b+2): the positions of batch b+1 are in
+            stage_values(b + 1);
+            cp_async_wait<2>();        // all but P(b+2), V(b+1): batch b is complete
         } else {
-            cp_async_wait<0>();
+            stage(b + 1);
+            cp_async_wait<1>();
         }
         worker_sync<LPV>(mask);
-        const int4 *mt = meta[w][b & 1];
+        const int4 *mt = meta[w][b % NBUF];
 
         float4 x[2][U][NT];
         int4 e[2][U];
