@@ -480,8 +480,13 @@ def run_b200(args, rank, local_rank, world):
             rec["compulsory_frac"] = cb / (ms * 1e-3) / 1e9 / peak if ms else None
         d = dram.get(o) if dram else None
         if d and ms and world == 1:
-            # DRAM bytes per nonzero from the quarter-size ncu capture, scaled by this run's nonzeros
+            # DRAM bytes per nonzero from the quarter-size ncu capture, scaled by this run's nonzeros; the
+            # output traffic of B*^S grows with the number of (column block, row) runs instead
             db = d["dram_bytes_per_nnz"] * shard.nnz
+            if o == "dsmultT" and plan_info and "dram_bytes_per_row_run" in d:
+                db += d["dram_bytes_per_row_run"] * plan_info["row_runs"]
+                if overwrite:
+                    db -= d.get("overwrite_saves_bytes_per_touched_row", 0) * plan_info["touched_rows"]
             rec["dram_bytes"] = db
             rec["dram_frac"] = db / (ms * 1e-3) / 1e9 / peak
             rec["l2_frac"] = d.get("lts_throughput_frac")

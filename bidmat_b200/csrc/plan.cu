@@ -40,6 +40,7 @@ struct bidmat_b200_plan {
     std::vector<int> block_c0, block_nch;
     int nchunks = 0, nruns = 0, ngroups = 0, nslots = 0, nclear = 0;
     long long touched_rows = 0;
+    long long row_runs = 0;        // runs of equal (column block, row): each one updates its output column once
     size_t bytes = 0;
 };
 
@@ -103,7 +104,7 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
     {
         const int ntiles = (int)((n + kSortTile - 1) / kSortTile);
         const size_t need = 6 * pad256(n * 4) + pad256((size_t)256 * ntiles * 4) + pad256(256 * kSortScanSegs * 4) +
-                            pad256(4096) + pad256((size_t)m * 4) + 4096;
+                            pad256(4096) + pad256((size_t)m * 4) + 8192;
         WorkspaceLease ws(need, st);
         PLAN_CK(ws.err);
         unsigned *keys[2] = {ws.take<unsigned>(n), ws.take<unsigned>(n)};
@@ -113,18 +114,23 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
         int *totals = ws.take<int>(256 * kSortScanSegs);
         int *offsets = ws.take<int>(1024);
         int *first_block = ws.take<int>((size_t)m);
+        unsigned long long *d_nruns = ws.take<unsigned long long>(1);
         run_rowsort<int>(nnz, lay.passes, SortKeySpec{lay.colshift, lay.rowbits}, Bir, Bic, nullptr, keys, cols, vals,
                          p->keys, p->cols, p->perm, counts, totals, st);
         PLAN_CK(cudaGetLastError());
         block_offsets_kernel<<<(lay.nblocks + 256) / 256, 256, 0, st>>>(nnz, lay.nblocks, lay.rowbits, p->keys, offsets);
         PLAN_CK(cudaMemsetAsync(first_block, 0x7f, (size_t)m * 4, st));      // kNoBlock in every entry
+        PLAN_CK(cudaMemsetAsync(d_nruns, 0, sizeof(unsigned long long), st));
         plan_first_block_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(nnz, p->keys, lay.rowbits, lay.rowmask,
-                                                                           first_block);
+                                                                           first_block, d_nruns);
         g_launches += 2;
         h_first.resize((size_t)m);
         PLAN_CK(cudaMemcpyAsync(h_off.data(), offsets, sizeof(int) * (lay.nblocks + 1), cudaMemcpyDeviceToHost, st));
         PLAN_CK(cudaMemcpyAsync(h_first.data(), first_block, sizeof(int) * (size_t)m, cudaMemcpyDeviceToHost, st));
+        unsigned long long h_nruns = 0;
+        PLAN_CK(cudaMemcpyAsync(&h_nruns, d_nruns, sizeof(h_nruns), cudaMemcpyDeviceToHost, st));
         PLAN_CK(cudaStreamSynchronize(st));
+        p->row_runs = (long long)h_nruns;
     }
 
     if (env_int("BIDMAT_B200_PLAN_SCATTER", 0)) {
@@ -154,27 +160,24 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
     const size_t nb_entries = (size_t)total + (size_t)lay.nblocks;      // nch + 1 boundaries per block
     std::vector<int> h_start(nb_entries);
     std::vector<unsigned> h_kfirst(nb_entries), h_kprev(nb_entries);
-    std::vector<int> h_fcol(nb_entries);
     {
-        WorkspaceLease ws(4 * pad256(nb_entries * 4) + 1024, st);
+        WorkspaceLease ws(3 * pad256(nb_entries * 4) + 1024, st);
         PLAN_CK(ws.err);
         int *d_start = ws.take<int>(nb_entries);
         unsigned *d_first = ws.take<unsigned>(nb_entries);
         unsigned *d_prev = ws.take<unsigned>(nb_entries);
-        int *d_fcol = ws.take<int>(nb_entries);
         for (int b = 0; b < lay.nblocks; b++) {
             const int nch = p->block_nch[b];
             if (nch == 0) continue;
             const size_t e0 = (size_t)p->block_c0[b] + b;
-            plan_bounds_kernel<<<(nch + 256) / 256, 256, 0, st>>>(h_off[b], h_off[b + 1], T[b], nch, p->keys, p->cols,
-                                                                  d_start + e0, d_first + e0, d_prev + e0, d_fcol + e0);
+            plan_bounds_kernel<<<(nch + 256) / 256, 256, 0, st>>>(h_off[b], h_off[b + 1], T[b], nch, p->keys,
+                                                                  d_start + e0, d_first + e0, d_prev + e0);
             g_launches += 1;
         }
         PLAN_CK(cudaGetLastError());
         PLAN_CK(cudaMemcpyAsync(h_start.data(), d_start, nb_entries * 4, cudaMemcpyDeviceToHost, st));
         PLAN_CK(cudaMemcpyAsync(h_kfirst.data(), d_first, nb_entries * 4, cudaMemcpyDeviceToHost, st));
         PLAN_CK(cudaMemcpyAsync(h_kprev.data(), d_prev, nb_entries * 4, cudaMemcpyDeviceToHost, st));
-        PLAN_CK(cudaMemcpyAsync(h_fcol.data(), d_fcol, nb_entries * 4, cudaMemcpyDeviceToHost, st));
         PLAN_CK(cudaStreamSynchronize(st));
     }
 
@@ -210,25 +213,6 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
                 d.w = tail ? -2 : -1;
             }
             h_desc[(size_t)p->block_c0[b] + c] = d;
-        }
-        // Chunks that lie inside ONE long row (first key == last key, cut at both ends or at
-        // one) gather a contiguous range of source columns.  The workers of a CTA take
-        // consecutive descriptors, so such chunks are ordered by their first source column
-        // instead of by row: the workers of one CTA then walk the same columns of the dense
-        // operand for different rows at the same time and share them through L1.  Only the
-        // order of the descriptors changes; slots and runs stay attached to their chunks.
-        if (env_int("BIDMAT_B200_PLAN_COLORDER", 1)) {
-            std::vector<int> pos;
-            for (int c = 0; c < nch; c++) {
-                const size_t e = e0 + c;
-                const int4 &d = h_desc[(size_t)p->block_c0[b] + c];
-                if (h_kfirst[e] == h_kprev[e + 1] && (d.z >= 0 || d.w != -1)) pos.push_back(c);
-            }
-            std::vector<int> order(pos);
-            std::stable_sort(order.begin(), order.end(), [&](int a, int c2) { return h_fcol[e0 + a] < h_fcol[e0 + c2]; });
-            std::vector<int4> moved(pos.size());
-            for (size_t i = 0; i < pos.size(); i++) moved[i] = h_desc[(size_t)p->block_c0[b] + order[i]];
-            for (size_t i = 0; i < pos.size(); i++) h_desc[(size_t)p->block_c0[b] + pos[i]] = moved[i];
         }
     }
     p->nslots = slot;
@@ -425,7 +409,7 @@ int bidmat_b200_plan_info(bidmat_b200_plan_t p, long long *out, int count) {
     if (!p || p->magic != kPlanMagic || !out || count < 0) return (int)cudaErrorInvalidValue;
     const long long v[BIDMAT_B200_PLAN_INFO_COUNT] = {
         p->nnz, p->ncols, p->m, p->k, p->elem, p->lay.nblocks, p->nchunks, p->nruns, p->nslots,
-        p->nclear, p->touched_rows, (long long)p->bytes};
+        p->nclear, p->touched_rows, (long long)p->bytes, p->row_runs};
     for (int i = 0; i < count && i < BIDMAT_B200_PLAN_INFO_COUNT; i++) out[i] = v[i];
     return 0;
 }

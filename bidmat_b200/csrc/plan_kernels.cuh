@@ -19,14 +19,12 @@ namespace bidmat {
 // the run of equal keys that contains it, unless that run began at or before the
 // previous nominal boundary (then the run is longer than a chunk and is cut at
 // the nominal position).  Every chunk is non-empty and shorter than 2T.
-// Outputs, for c in [0, nch]: start[c], the key at start[c] (first[c]), the key just
-// before it (prev[c]) and the source column at start[c] (fcol[c]); c = nch describes
-// the end of the block.
+// Outputs, for c in [0, nch]: start[c], the key at start[c] (first[c]) and the key
+// just before it (prev[c]); c = nch describes the end of the block.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-plan_bounds_kernel(int lo, int hi, int T, int nch, const unsigned *__restrict__ keys, const int *__restrict__ cols,
-                   int *__restrict__ start, unsigned *__restrict__ first, unsigned *__restrict__ prev,
-                   int *__restrict__ fcol) {
+plan_bounds_kernel(int lo, int hi, int T, int nch, const unsigned *__restrict__ keys,
+                   int *__restrict__ start, unsigned *__restrict__ first, unsigned *__restrict__ prev) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c > nch) return;
     int b;
@@ -45,7 +43,6 @@ plan_bounds_kernel(int lo, int hi, int T, int nch, const unsigned *__restrict__ 
     start[c] = b;
     first[c] = (b < hi) ? __ldg(keys + b) : 0xffffffffu;
     prev[c] = (b > lo) ? __ldg(keys + b - 1) : 0xffffffffu;
-    fcol[c] = (b < hi) ? __ldg(cols + b) : 0x7fffffff;
 }
 
 // vals[j] = data[perm[j]]: the values of a call, brought into the plan's order.
@@ -113,13 +110,18 @@ plan_verify_kernel(long long n, const int *__restrict__ perm, const unsigned *__
 constexpr int kNoBlock = 0x7f7f7f7f;
 __global__ void __launch_bounds__(256)
 plan_first_block_kernel(long long n, const unsigned *__restrict__ keys, int rowbits, unsigned rowmask,
-                        int *__restrict__ first_block) {
+                        int *__restrict__ first_block, unsigned long long *__restrict__ nruns) {
     const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= n) return;
-    const unsigned key = __ldg(keys + j);
-    // only the first nonzero of a run needs to vote
-    if (j > 0 && __ldg(keys + j - 1) == key) return;
-    atomicMin(first_block + (key & rowmask), (int)(key >> rowbits));
+    // only the first nonzero of a run (one row inside one column block) needs to vote
+    bool start = false;
+    unsigned key = 0;
+    if (j < n) {
+        key = __ldg(keys + j);
+        start = (j == 0) || (__ldg(keys + j - 1) != key);
+    }
+    if (start) atomicMin(first_block + (key & rowmask), (int)(key >> rowbits));
+    const unsigned bal = __ballot_sync(0xffffffffu, start);
+    if ((threadIdx.x & 31) == 0 && bal) atomicAdd(nruns, (unsigned long long)__popc(bal));   // number of runs
 }
 
 // Marks (bit 31 of the key) every nonzero that belongs to the first block of its

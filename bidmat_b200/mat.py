@@ -116,7 +116,7 @@ class TransposedPlan:
 
     OVERWRITE = 1
     _INFO = ("nnz", "ncols", "m", "k", "elem_bytes", "blocks", "chunks", "split_runs", "slots", "cleared_rows",
-             "touched_rows", "bytes")
+             "touched_rows", "bytes", "row_runs")
 
     def __init__(self, k, S=None, elem_bytes=4, stream=None, m=None, ncols=None, pir=None, pic=None):
         """From a GSMat `S`, or from raw device tensors pir / pic of an m x ncols structure."""

@@ -167,8 +167,9 @@ BIDMAT_B200_API int bidmat_b200_dsmultT_planned_f64(bidmat_b200_plan_t plan, int
 BIDMAT_B200_API int bidmat_b200_plan_verify(bidmat_b200_plan_t plan, int ncols, int nnz, const int *Bir,
                                             const int *Bic, bidmat_stream_t stream);
 /* out[0..count): nnz, ncols, m, nrows, elem_bytes, column blocks, chunks, split runs, slots,
- * rows cleared by an overwriting call, rows named by at least one nonzero, device bytes held. */
-#define BIDMAT_B200_PLAN_INFO_COUNT 12
+ * rows cleared by an overwriting call, rows named by at least one nonzero, device bytes held,
+ * (column block, row) runs (each updates its output column once per call). */
+#define BIDMAT_B200_PLAN_INFO_COUNT 13
 BIDMAT_B200_API int bidmat_b200_plan_info(bidmat_b200_plan_t plan, long long *out, int count);
 /* Copies to the device array `bitmap` (ceil(m/32) words, caller-owned) which rows of S hold a
  * nonzero: bit r%32 of word r/32 is set for such a row r.  Stream-ordered. */

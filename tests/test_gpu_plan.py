@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 
 OVERWRITE = 1
 INFO = ("nnz", "ncols", "m", "k", "elem_bytes", "blocks", "chunks", "split_runs", "slots", "cleared_rows",
-        "touched_rows", "bytes")
+        "touched_rows", "bytes", "row_runs")
 
 
 class Plan:
