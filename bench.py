@@ -437,7 +437,8 @@ def run_b200(args, rank, local_rank, world):
     value = 3 * 2.0 * k * nnz_total / (ms_per_step * 1e-3) / 1e9
     overwrite = bool(st.overwrite)
     allreduce_kind = (None if world == 1 else
-                      ("library kernel over NVLink peer memory, touched rows only" if st.touched is not None
+                      ("library kernel through the NVSwitch (multimem.ld_reduce / multimem.st)" if st.mc else
+                       "library kernel over NVLink peer memory, touched rows only" if st.touched is not None
                        else "library kernel over NVLink peer memory") if st.peer is not None else "NCCL")
 
     extras = None
@@ -757,8 +758,12 @@ def run_e2e(args, problem, shard, B_local, dev, rank, world, group):
     d_Ain = d_A[a0:a1] if world == 1 else torch.empty((a1 - a0, k), dtype=torch.float32, device=dev)
     G = GMat(torch.empty((m, k), dtype=torch.float32, device=dev))
 
+    phases = {}
+
     def one():
         evs = []
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        marks[0].record(main)
         with torch.cuda.stream(up):
             d_Ain.copy_(hA, non_blocking=True)
             ev_a = torch.cuda.Event(); ev_a.record(up)
@@ -770,6 +775,7 @@ def run_e2e(args, problem, shard, B_local, dev, rank, world, group):
         if group is not None:
             dist.all_gather_into_tensor(d_A, d_Ain, group=group)     # the model reaches every GPU over NVLink
         A = GMat(d_A)
+        marks[1].record(main)                           # the whole model is on the device
         G.clear()
         for ch, dch, e in zip(chunks, dchunks, evs):
             main.wait_event(e)
@@ -788,13 +794,17 @@ def run_e2e(args, problem, shard, B_local, dev, rank, world, group):
                 hP[ch["j0"]:ch["j1"]].copy_(P.pdata, non_blocking=True)
                 P.pdata.record_stream(down)
             B.maddT(S, G)                               # G += B *^ S
+        marks[2].record(main)                           # all chunks multiplied
         if group is not None:
             dist.all_reduce(G.t, op=dist.ReduceOp.SUM, group=group)
-        done = torch.cuda.Event(); done.record(main)
+        marks[3].record(main)                           # G summed over the ranks
         with torch.cuda.stream(down):
-            down.wait_event(done)
+            down.wait_event(marks[3])
             hG.copy_(G.t[a0:a1], non_blocking=True)
+            marks[4].record(down)                       # everything is back on the host
         torch.cuda.synchronize()
+        for i, name in enumerate(("model_upload_and_allgather", "chunks", "allreduce", "last_downloads")):
+            phases[name] = marks[i].elapsed_time(marks[i + 1])
 
     one()  # warm-up (allocator, scratch pool)
     torch.cuda.synchronize()
@@ -830,7 +840,8 @@ def run_e2e(args, problem, shard, B_local, dev, rank, world, group):
             "ms_per_step": float(ms[0]), "steps": args.e2e_steps,
             "h2d_bytes_per_step": int(bytes_[0]), "d2h_bytes_per_step": int(bytes_[1]),
             "pcie_gbs": pcie, "pcie_bound_ms": bound_ms, "ms_over_pcie_bound": float(ms[0]) / bound_ms,
-            "chunks_per_rank": len(chunks), "verified": bool(rel <= 1.0 and np.isfinite(rel)),
+            "chunks_per_rank": len(chunks), "phases_ms_rank0_last_step": phases,
+            "verified": bool(rel <= 1.0 and np.isfinite(rel)),
             "verified_rel_err_over_tolerance": rel,
             "api": "GMat * GSMat, DDS(GMat, GMat, GSMat), GMat.maddT(GSMat) per column chunk with pinned host operands; "
                    "uploads and downloads on their own streams, overlapped with the products"}

@@ -58,8 +58,12 @@ peer_sum_kernel(PeerPtrs peers, long long v_begin, long long v_end) {
 template <int W>
 __global__ void __launch_bounds__(256)
 peer_sum_rows_kernel(PeerPtrs peers, long long v_begin, long long v_end, int vec_per_row,
-                     const unsigned *__restrict__ touched, long long words) {
+                     const unsigned *__restrict__ touched, long long words, int hint) {
+    // hint: every access carries an L2 evict_first policy, so that the partials streaming
+    // through the L2 of their home GPU do not push out what A*S and DDS, which run at the
+    // same time, keep there
     constexpr int UNROLL = (W <= 4) ? 4 : 2;
+    const unsigned long long pol = l2_policy_evict_first();
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long v0 = v_begin + (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < v_end; v0 += stride * UNROLL) {
         float4 x[UNROLL][W];
@@ -72,8 +76,8 @@ peer_sum_rows_kernel(PeerPtrs peers, long long v_begin, long long v_end, int vec
 #pragma unroll
             for (int r = 0; r < W; r++) {
                 const bool wrote = (__ldg(touched + r * words + w) >> bit) & 1u;
-                x[u][r] = (v < v_end && wrote) ? reinterpret_cast<const float4 *>(peers.p[r])[v]
-                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 *src = reinterpret_cast<const float4 *>(peers.p[r]) + v;
+                x[u][r] = (v < v_end && wrote) ? (hint ? ld_f4_policy(src, pol) : *src) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
 #pragma unroll
@@ -84,7 +88,42 @@ peer_sum_rows_kernel(PeerPtrs peers, long long v_begin, long long v_end, int vec
 #pragma unroll
             for (int r = 1; r < W; r++) { s.x += x[u][r].x; s.y += x[u][r].y; s.z += x[u][r].z; s.w += x[u][r].w; }
 #pragma unroll
-            for (int r = 0; r < W; r++) reinterpret_cast<float4 *>(peers.p[r])[v] = s;
+            for (int r = 0; r < W; r++) {
+                float4 *dst = reinterpret_cast<float4 *>(peers.p[r]) + v;
+                if (hint) st_f4_policy(dst, s, pol); else *dst = s;
+            }
+        }
+    }
+}
+
+// The same sum through the NVSwitch: `mc` is a multicast address that maps the buffers of
+// all ranks.  multimem.ld_reduce makes the switch fetch this rank's slice from every GPU and
+// add it on the way (one load instead of W, 1/W of the inbound traffic); multimem.st stores
+// the total into every rank's buffer at once (one store instead of W, 1/W of the outbound
+// traffic).  Per GPU and direction about half as many bytes cross NVLink as with peer loads
+// and stores.  One GPU reduces each element and all receive its result, so the ranks end
+// bit-identical; the order of the additions inside the switch is the hardware's.
+__global__ void __launch_bounds__(256)
+mc_sum_kernel(float *mc, long long v_begin, long long v_end) {
+    constexpr int UNROLL = 4;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    float4 *p = reinterpret_cast<float4 *>(mc);
+    for (long long v0 = v_begin + (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < v_end; v0 += stride * UNROLL) {
+        float4 x[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            const long long v = v0 + u * stride;
+            x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (v < v_end)
+                asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(x[u].x), "=f"(x[u].y), "=f"(x[u].z), "=f"(x[u].w) : "l"(p + v) : "memory");
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            const long long v = v0 + u * stride;
+            if (v < v_end)
+                asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                             ::"l"(p + v), "f"(x[u].x), "f"(x[u].y), "f"(x[u].z), "f"(x[u].w) : "memory");
         }
     }
 }
@@ -108,6 +147,24 @@ int peer_args(int world, int rank, const unsigned long long *peer_addresses, lon
 
 }  // namespace
 
+extern "C" int bidmat_b200_mc_allreduce_sum(int world, int rank, void *multicast_address, long long count, int ctas,
+                                            bidmat_stream_t stream) {
+    if (world < 1 || rank < 0 || rank >= world || count < 0 || count % 4 != 0 || !multicast_address ||
+        (reinterpret_cast<uintptr_t>(multicast_address) & 15u))
+        return (int)cudaErrorInvalidValue;
+    if (count == 0 || world == 1) return 0;
+    const long long nvec = count / 4;
+    const long long per = (nvec + world - 1) / world;
+    const long long v_begin = per * rank < nvec ? per * rank : nvec;
+    const long long v_end = v_begin + per < nvec ? v_begin + per : nvec;
+    if (v_end <= v_begin) return 0;
+    if (ctas <= 0) ctas = 32;
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : cudaStreamPerThread;
+    mc_sum_kernel<<<ctas, 256, 0, st>>>(static_cast<float *>(multicast_address), v_begin, v_end);
+    g_launches += 1;
+    return (int)cudaGetLastError();
+}
+
 extern "C" int bidmat_b200_peer_allreduce_sum_rows(int world, int rank, const unsigned long long *peer_addresses,
                                                    int k, long long m, const unsigned *touched, int ctas,
                                                    bidmat_stream_t stream) {
@@ -120,10 +177,11 @@ extern "C" int bidmat_b200_peer_allreduce_sum_rows(int world, int rank, const un
     if (ctas <= 0) ctas = (world <= 2) ? 64 : (world <= 4) ? 48 : 32;
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : cudaStreamPerThread;
     const long long words = (m + 31) / 32;
+    const int hint = env_int("BIDMAT_B200_PEER_HINT", 0);
     switch (world) {
-        case 2: peer_sum_rows_kernel<2><<<ctas, 256, 0, st>>>(pp, v_begin, v_end, k / 4, touched, words); break;
-        case 4: peer_sum_rows_kernel<4><<<ctas, 256, 0, st>>>(pp, v_begin, v_end, k / 4, touched, words); break;
-        case 8: peer_sum_rows_kernel<8><<<ctas, 256, 0, st>>>(pp, v_begin, v_end, k / 4, touched, words); break;
+        case 2: peer_sum_rows_kernel<2><<<ctas, 256, 0, st>>>(pp, v_begin, v_end, k / 4, touched, words, hint); break;
+        case 4: peer_sum_rows_kernel<4><<<ctas, 256, 0, st>>>(pp, v_begin, v_end, k / 4, touched, words, hint); break;
+        case 8: peer_sum_rows_kernel<8><<<ctas, 256, 0, st>>>(pp, v_begin, v_end, k / 4, touched, words, hint); break;
         default: return (int)cudaErrorInvalidValue;
     }
     g_launches += 1;

@@ -420,6 +420,16 @@ int bidmat_b200_plan_touched_rows(bidmat_b200_plan_t p, unsigned *bitmap, bidmat
                                 cudaMemcpyDeviceToDevice, as_stream(stream));
 }
 
+int bidmat_b200_plan_clear_untouched(bidmat_b200_plan_t p, int nrows, void *C, bidmat_stream_t stream) {
+    if (!plan_ok(p) || !C || nrows != p->k) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = as_stream(stream);
+    const unsigned blocks = (unsigned)(((size_t)p->m * 32 + 255) / 256);
+    if (p->elem == 4) plan_clear_untouched_kernel<float><<<blocks, 256, 0, st>>>(p->k, p->m, p->touched, static_cast<float *>(C));
+    else plan_clear_untouched_kernel<double><<<blocks, 256, 0, st>>>(p->k, p->m, p->touched, static_cast<double *>(C));
+    g_launches += 1;
+    return (int)cudaGetLastError();
+}
+
 int bidmat_b200_plan_destroy(bidmat_b200_plan_t p) {
     if (!p) return 0;
     if (p->magic != kPlanMagic) return (int)cudaErrorInvalidValue;

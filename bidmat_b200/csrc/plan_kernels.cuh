@@ -157,6 +157,18 @@ plan_clear_rows_kernel(int k, int nrows_listed, const int *__restrict__ rows, S 
     for (int i = threadIdx.x & 31; i < k; i += 32) o[i] = (S)0;
 }
 
+// Zeroes the output columns of the rows that no nonzero names (bitmap `touched`): one
+// worker of 32 lanes per row.
+template <typename S>
+__global__ void __launch_bounds__(256)
+plan_clear_untouched_kernel(int k, int m, const unsigned *__restrict__ touched, S *__restrict__ O) {
+    const int row = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    if (row >= m) return;
+    if ((__ldg(touched + (row >> 5)) >> (row & 31)) & 1u) return;
+    S *o = O + (size_t)row * k;
+    for (int i = threadIdx.x & 31; i < k; i += 32) o[i] = (S)0;
+}
+
 __device__ __forceinline__ void prefetch_l2(const void *p) {
     asm volatile("prefetch.global.L2 [%0];\n" ::"l"(p));
 }

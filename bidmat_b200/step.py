@@ -94,7 +94,9 @@ class PathStep:
         if self.peer is None:
             self.G = torch.zeros((shard.m, k), dtype=torch.float32, device=dev)
         # clear G every step?  Not when the plan overwrites and nobody reads the untouched rows.
-        self.overwrite = self.plan is not None and (group is None or (self.peer is not None and self.touched is not None))
+        self.mc = self.peer is not None and bool(self.peer["mc"])
+        self.overwrite = self.plan is not None and (group is None or (self.peer is not None and
+                                                                     (self.touched is not None or self.mc)))
 
     def _setup_peer_memory(self, shard, k, dev, group):
         import ctypes
@@ -112,9 +114,15 @@ class PathStep:
             "comm": torch.cuda.Stream(device=dev, priority=-1),
             "flag": torch.zeros(1, dtype=torch.float32, device=dev),
             "ctas": int(os.environ.get("BIDMAT_B200_PEER_CTAS", "0")),
+            "mc": 0,
         }
+        # a multicast mapping of the buffers (NVSwitch): the sum can then run inside the switch
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        if mc and self.plan is not None and int(os.environ.get("BIDMAT_B200_PEER_MC", "1")):
+            self.peer["mc"] = mc
         self.G.zero_()
-        if self.plan is not None and k % 4 == 0 and not int(os.environ.get("BIDMAT_B200_PEER_DENSE", "0")):
+        if (self.plan is not None and k % 4 == 0 and not self.peer["mc"]
+                and not int(os.environ.get("BIDMAT_B200_PEER_DENSE", "0"))):
             # every rank's touched-row bitmap, rank 0 first: exchanged once, the structure does not change
             mine = self.plan.touched_rows()
             allmaps = torch.empty(world * mine.numel(), dtype=torch.int32, device=dev)
@@ -151,6 +159,11 @@ class PathStep:
             if not self.overwrite:
                 self.G.zero_()   # GMat.GSMultT clears the output (GMat.scala:1082)
             if self.plan is not None:
+                if self.mc:
+                    # the switch adds whole buffers: rows this rank does not write must be zero
+                    # (they hold the previous sum); the rows it writes are overwritten below
+                    _ck(_L.bidmat_b200_plan_clear_untouched(self.plan.handle, self.k, self.G.data_ptr(),
+                                                            self.stream.cuda_stream), "plan_clear_untouched")
                 _ck(_L.bidmat_b200_dsmultT_planned(self.plan.handle, self.k, S.n, S.nnz, self.B.data_ptr(),
                                                    vals.data_ptr(), self.G.data_ptr(),
                                                    1 if self.overwrite else 0, self.stream.cuda_stream), "dsmultT (planned)")
@@ -175,7 +188,10 @@ class PathStep:
             before = dist.all_reduce(pr["flag"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
             with torch.cuda.stream(pr["comm"]):
                 before.wait()
-                if self.touched is not None:
+                if self.mc:
+                    _ck(_L.bidmat_b200_mc_allreduce_sum(pr["world"], pr["rank"], pr["mc"], self.G.numel(), pr["ctas"],
+                                                        pr["comm"].cuda_stream), "mc_allreduce_sum")
+                elif self.touched is not None:
                     _ck(_L.bidmat_b200_peer_allreduce_sum_rows(pr["world"], pr["rank"], pr["addrs"], self.k, self.S.m,
                                                                self.touched.data_ptr(), pr["ctas"],
                                                                pr["comm"].cuda_stream), "peer_allreduce_sum_rows")

@@ -175,6 +175,11 @@ BIDMAT_B200_API int bidmat_b200_plan_info(bidmat_b200_plan_t plan, long long *ou
  * nonzero: bit r%32 of word r/32 is set for such a row r.  Stream-ordered. */
 BIDMAT_B200_API int bidmat_b200_plan_touched_rows(bidmat_b200_plan_t plan, unsigned *bitmap,
                                                   bidmat_stream_t stream);
+/* Zeroes the columns of C (nrows x m, of the plan's element type) that no nonzero of S names: with
+ * BIDMAT_B200_PLAN_OVERWRITE before it, C then equals the product everywhere without a full clear
+ * (what a sum over whole buffers, e.g. bidmat_b200_mc_allreduce_sum, needs).  Stream-ordered. */
+BIDMAT_B200_API int bidmat_b200_plan_clear_untouched(bidmat_b200_plan_t plan, int nrows, void *C,
+                                                     bidmat_stream_t stream);
 BIDMAT_B200_API int bidmat_b200_plan_destroy(bidmat_b200_plan_t plan);
 
 /* A*S without any allocation.  No counterpart in the reference: BIDMat's
@@ -233,6 +238,17 @@ BIDMAT_B200_API int bidmat_b200_peer_allreduce_sum_rows(int world, int rank,
                                                         const unsigned long long *peer_addresses, int k,
                                                         long long m, const unsigned *touched, int ctas,
                                                         bidmat_stream_t stream);
+
+/* The same sum through the NVSwitch, for buffers that are bound to a multicast object:
+ * multicast_address is the multicast mapping of the ranks' buffers of `count` floats (count a
+ * multiple of 4).  The calling rank reduces its 1/world slice with multimem.ld_reduce (the switch
+ * fetches it from every GPU and adds on the way) and stores the total into all buffers with
+ * multimem.st, so about half as many bytes cross NVLink per GPU and direction as with peer loads
+ * and stores, and all ranks end bit-identical (the order of the additions is the switch's).
+ * Whole buffers are summed: rows a rank did not write must hold zeros
+ * (bidmat_b200_plan_clear_untouched).  Same ordering rules as bidmat_b200_peer_allreduce_sum. */
+BIDMAT_B200_API int bidmat_b200_mc_allreduce_sum(int world, int rank, void *multicast_address, long long count,
+                                                 int ctas, bidmat_stream_t stream);
 
 /* Structure helpers on the device (the steps BIDMat performs around the path
  * with cuSPARSE csr2coo and a host loop: GSMat.fromSMat, GSMat.scala:639, and

@@ -40,18 +40,30 @@ def _worker(rank, world, port, q):
         B_local = p.B[shard.col0:shard.col1].contiguous()
         stream = torch.cuda.Stream(device=dev)
         outs = {}
+        kinds = {}
         with torch.cuda.stream(stream):
-            for mode in (False, True):
-                st = pstep.PathStep(p.k, shard, p.A, B_local, stream, dist.group.WORLD, peer_reduce=mode)
-                for _ in range(2):        # twice: the buffers are reused from step to step
+            # NCCL; the library's sum through the switch (where the buffers have a multicast
+            # mapping); the library's sum over peer loads and stores of the touched rows
+            for mode, peer, mc in (("nccl", False, "0"), ("switch", True, "1"), ("rows", True, "0")):
+                os.environ["BIDMAT_B200_PEER_MC"] = mc
+                st = pstep.PathStep(p.k, shard, p.A, B_local, stream, dist.group.WORLD, peer_reduce=peer)
+                kinds[mode] = "switch" if st.mc else ("rows" if st.touched is not None else "nccl" if st.peer is None else "dense")
+                for _ in range(3):        # several steps: the buffers are reused from step to step
                     st.run()
                 torch.cuda.synchronize()
                 dist.barrier()
                 outs[mode] = st.G.clone()
-        same_bits = torch.equal(outs[False], outs[True])      # two ranks: a + b in either implementation
-        other = outs[True].clone()
-        dist.broadcast(other, src=0)
-        same_across_ranks = torch.equal(other.view(torch.int32), outs[True].view(torch.int32))
+                st.close()
+        # two ranks: a + b in every implementation
+        same_bits = torch.equal(outs["nccl"], outs["switch"]) and torch.equal(outs["nccl"], outs["rows"])
+        same_across_ranks = True
+        for mode in ("switch", "rows"):
+            other = outs[mode].clone()
+            dist.broadcast(other, src=0)
+            same_across_ranks = same_across_ranks and torch.equal(other.view(torch.int32), outs[mode].view(torch.int32))
+        outs[True] = outs["rows"]
+        if rank == 0:
+            print("allreduce kinds exercised:", kinds, flush=True)
         if rank == 0:
             import oracle
             from util import RTOL_DSMULTT
