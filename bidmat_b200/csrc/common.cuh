@@ -77,36 +77,6 @@ template <int LPV> __device__ __forceinline__ unsigned worker_mask() {
     }
 }
 
-// L2 eviction policies (createpolicy) and 16-byte accesses that carry one.  evict_last on
-// the gathers of a dense operand keeps its popular columns in L2 while streams (index
-// lists, outputs, a concurrent sum over NVLink) pass through; evict_first marks a stream.
-__device__ __forceinline__ unsigned long long l2_policy_evict_last() {
-    unsigned long long pol;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-__device__ __forceinline__ unsigned long long l2_policy_evict_first() {
-    unsigned long long pol;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-__device__ __forceinline__ float4 ldg_f4_policy(const float4 *p, unsigned long long pol) {
-    float4 v;
-    asm volatile("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(pol));
-    return v;
-}
-__device__ __forceinline__ float4 ld_f4_policy(const float4 *p, unsigned long long pol) {
-    float4 v;
-    asm volatile("ld.global.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(pol) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_f4_policy(float4 *p, const float4 &v, unsigned long long pol) {
-    asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;"
-                 ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "l"(pol) : "memory");
-}
-
 constexpr int kThreads = 256;  // threads per CTA for every kernel here
 
 }  // namespace bidmat

@@ -258,8 +258,7 @@ template <int LPV> __device__ __forceinline__ void worker_sync(unsigned mask) {
     __syncwarp(mask);
 }
 
-// KEEP: the gathers of D carry an L2 evict_last policy (see common.cuh).
-template <int LPV, int NT, int U, int TPB, int MINB = 0, bool KEEP = false>
+template <int LPV, int NT, int U, int TPB, int MINB = 0>
 __global__ void __launch_bounds__(TPB, MINB)
 ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
                      const float *__restrict__ D, const float *__restrict__ val,
@@ -285,8 +284,6 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     const long long j1 = (j0 + chunk < hi) ? j0 + chunk : hi;
     const int nb = (int)((j1 - j0 + LPV - 1) / LPV);
     const float *Dl = D + lane * 4;        // this lane's first float4 inside any column
-    const unsigned long long keep = KEEP ? l2_policy_evict_last() : 0ull;
-    auto gather = [&](const float4 *p) -> float4 { return KEEP ? ldg_f4_policy(p, keep) : __ldg(p); };
 
     auto stage = [&](int buf, long long base) {
         const long long jj = base + lane;
@@ -357,7 +354,7 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
             e[0][u] = mt[u];
             const float4 *d = reinterpret_cast<const float4 *>(Dl + (size_t)e[0][u].x * K);
 #pragma unroll
-            for (int t = 0; t < NT; t++) x[0][u][t] = gather(d + t * LPV);
+            for (int t = 0; t < NT; t++) x[0][u][t] = __ldg(d + t * LPV);
         }
 #pragma unroll
         for (int g = 0; g < G; g++) {
@@ -367,7 +364,7 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
                     e[(g + 1) & 1][u] = mt[(g + 1) * U + u];
                     const float4 *d = reinterpret_cast<const float4 *>(Dl + (size_t)e[(g + 1) & 1][u].x * K);
 #pragma unroll
-                    for (int t = 0; t < NT; t++) x[(g + 1) & 1][u][t] = gather(d + t * LPV);
+                    for (int t = 0; t < NT; t++) x[(g + 1) & 1][u][t] = __ldg(d + t * LPV);
                 }
             }
 #pragma unroll
@@ -402,7 +399,7 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
 // then two plain xor steps finish, 9 shuffles per 8 nonzeros instead of 40.
 // After four such groups lane l holds the result of nonzero (l&3)*8 + (l>>2)
 // of the batch, and the 32 results go out as one 128-byte store.
-template <int NT, int TPB, bool ACCUM, bool KEEP = false>
+template <int NT, int TPB, bool ACCUM>
 __global__ void __launch_bounds__(TPB)
 dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
                       const float *__restrict__ A, const float *__restrict__ B,
@@ -423,8 +420,6 @@ dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     const int nb = (int)((j1 - j0 + LPV - 1) / LPV);
     const float *Al = A + lane * 4;
     const float *Bl = B + lane * 4;
-    const unsigned long long keep = KEEP ? l2_policy_evict_last() : 0ull;
-    auto gather = [&](const float4 *p) -> float4 { return KEEP ? ldg_f4_policy(p, keep) : __ldg(p); };
 
     auto stage = [&](int buf, long long base) {
         const long long jj = base + lane;
@@ -468,7 +463,7 @@ dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
             e[0][u] = mt[u];
             const float4 *a = reinterpret_cast<const float4 *>(Al + (size_t)e[0][u].x * K);
 #pragma unroll
-            for (int t = 0; t < NT; t++) x[0][u][t] = gather(a + t * LPV);
+            for (int t = 0; t < NT; t++) x[0][u][t] = __ldg(a + t * LPV);
         }
         float p[8];
 #pragma unroll
@@ -479,7 +474,7 @@ dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
                     e[(g + 1) & 1][u] = mt[(g + 1) * U + u];
                     const float4 *a = reinterpret_cast<const float4 *>(Al + (size_t)e[(g + 1) & 1][u].x * K);
 #pragma unroll
-                    for (int t = 0; t < NT; t++) x[(g + 1) & 1][u][t] = gather(a + t * LPV);
+                    for (int t = 0; t < NT; t++) x[(g + 1) & 1][u][t] = __ldg(a + t * LPV);
                 }
             }
 #pragma unroll

@@ -39,17 +39,9 @@ cudaError_t launch_ga(int k, long long nnz, const S *D, const S *val, const int 
             const int wpb = kFastThreads / s.lpv;
             dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
             ScopedSpan sp(label, st);
-            // BIDMAT_B200_L2KEEP=1: gathers with an L2 evict_last policy
-            static const int keep = env_int("BIDMAT_B200_L2KEEP", 0);
 #define CALL_FAST(LPV, NT, U, MINB)                                                                    \
-    do {                                                                                               \
-        if (keep)                                                                                      \
-            ga_chunk_fast_kernel<LPV, NT, U, kFastThreads, MINB, true><<<fgrid, kFastThreads, 0, st>>>( \
-                nnz, chunk, nchunks, D, val, gidx, seg, O, part, range, segmask);                      \
-        else                                                                                           \
-            ga_chunk_fast_kernel<LPV, NT, U, kFastThreads, MINB, false><<<fgrid, kFastThreads, 0, st>>>( \
-                nnz, chunk, nchunks, D, val, gidx, seg, O, part, range, segmask);                      \
-    } while (0)
+    ga_chunk_fast_kernel<LPV, NT, U, kFastThreads, MINB><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, D, val, \
+                                                                                        gidx, seg, O, part, range, segmask)
             // Last argument: minimum CTAs per SM given to the compiler, 0 = leave it to the
             // compiler (an explicit 1 makes it take 255 registers and halves the occupancy).
             // k = 256: five CTAs of 128 threads (<= 96 registers) measured 10 % faster than
@@ -99,14 +91,10 @@ cudaError_t launch_dds(int k, long long nnz, const S *A, const S *B, const int *
         if (fast_shape(k, s) && s.lpv == 32 && s.nt <= 2 && !env_int("BIDMAT_B200_GENERIC", 0)) {
             const int wpb = kFastThreads / 32;
             dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
-            static const int keep = env_int("BIDMAT_B200_L2KEEP", 0);
-            if (s.nt == 1) {
-                if (keep) dds_chunk_fast_kernel<1, kFastThreads, ACCUM, true><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
-                else dds_chunk_fast_kernel<1, kFastThreads, ACCUM, false><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
-            } else {
-                if (keep) dds_chunk_fast_kernel<2, kFastThreads, ACCUM, true><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
-                else dds_chunk_fast_kernel<2, kFastThreads, ACCUM, false><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
-            }
+            if (s.nt == 1)
+                dds_chunk_fast_kernel<1, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
+            else
+                dds_chunk_fast_kernel<2, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
             done = true;
         }
     }

@@ -116,9 +116,12 @@ class PathStep:
             "ctas": int(os.environ.get("BIDMAT_B200_PEER_CTAS", "0")),
             "mc": 0,
         }
-        # a multicast mapping of the buffers (NVSwitch): the sum can then run inside the switch
+        # A multicast mapping of the buffers (NVSwitch) lets the sum run inside the switch
+        # (BIDMAT_B200_PEER_MC=1).  Measured on 2, 4 and 8 GPUs it is no faster than peer loads and
+        # stores of the touched rows (what limits the step is the time A*S and DDS lose while any
+        # form of the sum runs beside them), so it is not the default.
         mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
-        if mc and self.plan is not None and int(os.environ.get("BIDMAT_B200_PEER_MC", "1")):
+        if mc and self.plan is not None and int(os.environ.get("BIDMAT_B200_PEER_MC", "0")):
             self.peer["mc"] = mc
         self.G.zero_()
         if (self.plan is not None and k % 4 == 0 and not self.peer["mc"]

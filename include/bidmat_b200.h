@@ -233,7 +233,8 @@ BIDMAT_B200_API int bidmat_b200_peer_allreduce_sum(int world, int rank, const un
  * so no rank has to clear its buffer between steps (columns it did not write may hold the
  * previous sum) and less crosses NVLink; columns nobody wrote are set to zero.  Together
  * with BIDMAT_B200_PLAN_OVERWRITE this removes the clearing of the k x m partial from the
- * step.  Same ordering rules as bidmat_b200_peer_allreduce_sum. */
+ * step.  ctas <= 0: 64 CTAs for 2 GPUs, 48 for 4 or 8.  Same ordering rules as
+ * bidmat_b200_peer_allreduce_sum. */
 BIDMAT_B200_API int bidmat_b200_peer_allreduce_sum_rows(int world, int rank,
                                                         const unsigned long long *peer_addresses, int k,
                                                         long long m, const unsigned *touched, int ctas,
