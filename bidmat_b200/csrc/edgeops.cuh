@@ -61,34 +61,52 @@ segsum_chunk_kernel(long long nnz, long long nchunks, const S *__restrict__ P, c
     if (c >= nchunks) return;
     const long long j0 = c * CHUNK;
     const long long j1 = (j0 + CHUNK < nnz) ? j0 + CHUNK : nnz;
-    const int first = __ldg(seg + j0);
-    const bool head_open = (j0 > 0) && (__ldg(seg + j0 - 1) == first);
+    // everything the chunk needs is loaded first (ITEMS independent coalesced rows of keys and
+    // values, plus the two keys either side of the chunk), then summed from registers
+    int key[ITEMS];
+    S val[ITEMS];
+    const int last_key = __ldg(seg + j1 - 1);
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const long long j = j0 + (long long)i * 32 + lane;
+        const bool valid = j < j1;
+        // padding lanes get a key of their own (no segment contains them) and add nothing
+        key[i] = valid ? __ldg(seg + j) : ~last_key;
+        val[i] = valid ? __ldg(P + j) : (S)0;
+    }
+    const int first = __shfl_sync(0xffffffffu, key[0], 0);
+    const int before = (j0 > 0) ? __ldg(seg + j0 - 1) : ~first;
+    const int after = (j1 < nnz) ? __ldg(seg + j1) : ~last_key;
+    const bool head_open = before == first;
     int carry_key = first;
     S carry = 0;
 #pragma unroll
     for (int i = 0; i < ITEMS; i++) {
         const long long j = j0 + (long long)i * 32 + lane;
         const bool valid = j < j1;
-        // padding lanes get a key of their own (no segment contains them) and add nothing
-        const int key = valid ? __ldg(seg + j) : ~__ldg(seg + j1 - 1);
-        const int next = (valid && j + 1 < nnz) ? __ldg(seg + j + 1) : ~key;
-        S v = valid ? __ldg(P + j) : (S)0;
+        const int k_ = key[i];
+        // key of the next element: the next lane's, for lane 31 lane 0 of the next row, after the chunk `after`
+        int next = __shfl_down_sync(0xffffffffu, k_, 1);
+        const int next_row0 = __shfl_sync(0xffffffffu, (i + 1 < ITEMS) ? key[i + 1 < ITEMS ? i + 1 : i] : after, 0);
+        if (lane == 31) next = next_row0;
+        if (valid && j == j1 - 1) next = after;
+        S v = val[i];
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const S uv = __shfl_up_sync(0xffffffffu, v, d);
-            const int uk = __shfl_up_sync(0xffffffffu, key, d);
-            if (lane >= d && uk == key) v += uv;
+            const int uk = __shfl_up_sync(0xffffffffu, k_, d);
+            if (lane >= d && uk == k_) v += uv;
         }
-        if (key == carry_key) v += carry;          // the run that came in from the previous row of this chunk
-        const bool ends = valid && next != key;    // last element of its run
+        if (k_ == carry_key) v += carry;           // the run that came in from the previous row of this chunk
         const bool last = valid && j == j1 - 1;    // last element of the chunk
+        const bool ends = valid && next != k_;     // last element of its run
         if (ends) {
-            if (head_open && key == first) part[c * 2] = v;      // piece of the run that entered from the left
-            else B[key] += v;
+            if (head_open && k_ == first) part[c * 2] = v;       // piece of the run that entered from the left
+            else B[k_] += v;
         } else if (last) {
-            part[c * 2 + ((head_open && key == first) ? 0 : 1)] = v;   // the run goes on in the next chunk
+            part[c * 2 + ((head_open && k_ == first) ? 0 : 1)] = v;    // the run goes on in the next chunk
         }
-        const int k31 = __shfl_sync(0xffffffffu, key, 31);
+        const int k31 = __shfl_sync(0xffffffffu, k_, 31);
         const S v31 = __shfl_sync(0xffffffffu, v, 31);
         const bool e31 = __shfl_sync(0xffffffffu, (int)ends, 31) != 0;
         carry_key = k31;
