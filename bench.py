@@ -733,9 +733,20 @@ def run_e2e(args, problem, shard, B_local, dev, rank, world, group):
 
     # ---- host operands (pinned), prepared once: they are the inputs of every step
     pin = lambda t: t.cpu().pin_memory()
-    cb = gen.shard_columns(shard.jc, nchunks)
+    # Column chunks of equal nonzero count, except that the last regular chunk is cut 3 : 1 again:
+    # what is multiplied after the last upload has arrived delays the download of G, so the
+    # last chunk is a small one.
+    if nchunks >= 2:
+        fr = [i / float(nchunks) for i in range(nchunks)] + [(nchunks - 0.25) / nchunks, 1.0]
+        targets = torch.tensor([int(shard.nnz * f) for f in fr[1:-1]], dtype=shard.jc.dtype, device=shard.jc.device)
+        cuts = torch.searchsorted(shard.jc.contiguous(), targets).clamp_(0, shard.n).tolist()
+        cb = [0] + [int(c) for c in cuts] + [shard.n]
+        for i in range(1, len(cb)):
+            cb[i] = max(cb[i], cb[i - 1])
+    else:
+        cb = gen.shard_columns(shard.jc, nchunks)
     chunks = []
-    for c in range(nchunks):
+    for c in range(len(cb) - 1):
         c0, c1 = cb[c], cb[c + 1]
         j0, j1 = int(shard.jc[c0]), int(shard.jc[c1])
         if c1 <= c0:
