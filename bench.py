@@ -60,6 +60,7 @@ def parse_args():
     ap.add_argument("--no-verify", action="store_true")
     ap.add_argument("--no-plan", action="store_true", help="B*^S through the reference-signature entry point "
                     "(sorts on every call) instead of the prepared plan")
+    ap.add_argument("--no-fuse", action="store_true", help="A*S and DDS as two calls instead of the one-pass entry point")
     ap.add_argument("--nccl-allreduce", action="store_true",
                     help="several GPUs: sum the B*^S partials with NCCL instead of the library's peer-memory kernel")
     ap.add_argument("--no-kernel-timing", action="store_true",
@@ -155,6 +156,8 @@ def algorithmic_bytes(op, k, nnz, n, m):
 
 
 def compulsory_bytes(op, k, nnz, n, m, rows_touched, overwrite):
+    if op == "dsmult_dds":  # one pass: the index lists and the named columns of A cross once for both results
+        return 12 * nnz + 4 * k * rows_touched + 8 * k * n + 8 * nnz + 4 * k * n
     """What has to cross HBM at least once: the index and value lists, every dense
     column that is named once, and the output once (written) or twice (read and
     written, where the interface accumulates)."""
@@ -366,7 +369,9 @@ def run_b200(args, rank, local_rank, world):
     torch.cuda.synchronize()
     t_plan = time.perf_counter()
     st = pstep.PathStep(k, shard, problem.A, B_local, stream, group,
-                        peer_reduce=(world > 1 and not args.nccl_allreduce), use_plan=not args.no_plan)
+                        peer_reduce=(world > 1 and not args.nccl_allreduce), use_plan=not args.no_plan,
+                        fuse=not args.no_fuse)
+    fuse = st.fuse
     torch.cuda.synchronize()
     plan_ms = 1e3 * (time.perf_counter() - t_plan)
     plan_info = st.plan.info() if st.plan is not None else None
@@ -377,7 +382,7 @@ def run_b200(args, rank, local_rank, world):
             dist.barrier()
         torch.cuda.synchronize()
 
-    ops = ("dsmultT", "dsmult", "dds", "allreduce_exposed")
+    ops = ("dsmultT", "dsmult_dds", "allreduce_exposed") if fuse else ("dsmultT", "dsmult", "dds", "allreduce_exposed")
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
             st.run()
@@ -386,7 +391,7 @@ def run_b200(args, rank, local_rank, world):
         L.bidmat_b200_timing_enable(0 if args.no_kernel_timing else 1)
         sampler = ClockSampler(physical_index(local_rank))
         launches0 = L.bidmat_b200_launch_count()
-        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(ops) + 1)] for _ in range(args.steps)]
         sampler.start()
         barrier()
         t_start = torch.cuda.Event(enable_timing=True)
@@ -397,10 +402,13 @@ def run_b200(args, rank, local_rank, world):
             ev[s][0].record(stream)
             st.dsmultT_local(); ev[s][1].record(stream)
             work = st.allreduce_start()
-            st.dsmult(); ev[s][2].record(stream)
-            st.dds(); ev[s][3].record(stream)
+            if fuse:
+                st.dsmult_dds(); ev[s][2].record(stream)
+            else:
+                st.dsmult(); ev[s][2].record(stream)
+                st.dds(); ev[s][3].record(stream)
             st.wait(work)
-            ev[s][4].record(stream)
+            ev[s][len(ops)].record(stream)
         t_end.record(stream)
         barrier()
         clocks = sampler.stop()
@@ -410,7 +418,7 @@ def run_b200(args, rank, local_rank, world):
     op_ms = {o: sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(args.steps)) / args.steps
              for i, o in enumerate(ops)}
     kern = {}
-    for label in ("dsmult_ga_chunk", "dsmultT_ga_chunk", "dsmultT_permute", "dsmultT_rowsort", "ga_fixup", "dds_chunk",
+    for label in ("dsmult_dds_chunk", "dsmult_ga_chunk", "dsmultT_ga_chunk", "dsmultT_permute", "dsmultT_rowsort", "ga_fixup", "dds_chunk",
                   "sort_hist", "sort_scan", "sort_scatter"):
         ms, cnt = _lib.timing_read(label)
         kern[label] = {"launches_per_step": cnt / args.steps, "avg_ms": ms / cnt if cnt else None,
@@ -462,19 +470,23 @@ def run_b200(args, rank, local_rank, world):
     peak, peak_src = measured_peak()
     dram = load_dram_profile()
     roof_ops = {}
-    for o, label in (("dsmult", "dsmult_ga_chunk"), ("dds", "dds_chunk"), ("dsmultT", "dsmultT_ga_chunk")):
-        # algorithmic bytes of the rank's whole shard; the launches of one step together process it once
-        ab = algorithmic_bytes(o, k, shard.nnz, shard.n, m)
+    op_list = ((("dsmult_dds", "dsmult_dds_chunk", ("dsmult", "dds")),) if fuse else
+               (("dsmult", "dsmult_ga_chunk", ("dsmult",)), ("dds", "dds_chunk", ("dds",)))) + \
+              (("dsmultT", "dsmultT_ga_chunk", ("dsmultT",)),)
+    for o, label, parts in op_list:
+        # algorithmic bytes of the rank's whole shard (for the one-pass kernel: of both operations it
+        # computes); the launches of one step together process it once
+        ab = sum(algorithmic_bytes(q, k, shard.nnz, shard.n, m) for q in parts)
         ms = kern[label]["ms_per_step"]
         if o == "dsmultT" and world > 1:
             op_ms_max[o] += op_ms_max["allreduce_exposed"]   # the part of the allreduce that A*S and DDS did not hide
         rec = {"kernel": label, "kernel_ms": ms, "launches_per_step": kern[label]["launches_per_step"],
-               "algorithmic_bytes": ab,
+               "operations": list(parts), "algorithmic_bytes": ab,
                "achieved_gbs": ab / (ms * 1e-3) / 1e9 if ms else None,
                "frac": ab / (ms * 1e-3) / 1e9 / peak if ms else None,
                "op_ms_max_over_ranks": op_ms_max[o],
                "op_frac": ab / (op_ms_max[o] * 1e-3) / 1e9 / peak,
-               "op_gflops": 2.0 * k * nnz_total / (op_ms_max[o] * 1e-3) / 1e9}
+               "op_gflops": len(parts) * 2.0 * k * nnz_total / (op_ms_max[o] * 1e-3) / 1e9}
         if st_rows_touched is not None:
             cb = compulsory_bytes(o, k, shard.nnz, shard.n, m, st_rows_touched, overwrite and o == "dsmultT")
             rec["compulsory_bytes"] = cb
@@ -513,6 +525,8 @@ def run_b200(args, rank, local_rank, world):
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": workload_config(problem, args, world, {
+            "dsmult_dds_path": ("one pass over S for A*S and DDS (bidmat_b200_dsmult_dds_async): the gather of A's "
+                                "columns is shared" if fuse else "two calls (dsmult, dds)"),
             "dsmultT_path": ("reference-signature entry point (sorts every call)" if args.no_plan else
                              "prepared plan: structure sorted once outside the timed region (%.0f ms, %s bytes held), "
                              "values permuted every call, %s" % (plan_ms, plan_info["bytes"] if plan_info else "?",
@@ -579,6 +593,9 @@ def run_extras(args, problem, shard, B_local, st, dev, stream):
             assert err == 0, _lib.error_string(err)
         out["dsmultT_unprepared_ms"] = time_calls(dropin, stream, 3, 1)
         del G2
+        # (1b) A*S and DDS as two calls (what the one-pass entry point replaces)
+        out["dsmult_alone_ms"] = time_calls(st.dsmult, stream, 3, 1)
+        out["dds_alone_ms"] = time_calls(st.dds, stream, 3, 1)
 
     # (2) the reference's own CUDA kernels on the same operands, and an element-wise comparison at full size
     try:
@@ -792,14 +809,18 @@ def run_e2e(args, problem, shard, B_local, dev, rank, world, group):
             main.wait_event(e)
             S = GSMat.from_csc(m, ch["c1"] - ch["c0"], dch["jc"], dch["ir"], dch["data"])
             B = GMat(dch["B"])
-            C = A * S                                   # complete on return, like the BIDMat call
+            if args.no_fuse:
+                C = A * S                               # complete on return, like the BIDMat call
+            else:
+                C, P = A.GSMultDDS(B, S)                # A*S and DDS(A,B,S) in one pass over S
             done = torch.cuda.Event(); done.record(main)
             with torch.cuda.stream(down):
                 down.wait_event(done)
                 hC[ch["c0"]:ch["c1"]].copy_(C.t, non_blocking=True)
                 C.t.record_stream(down)                 # the copy outlives this chunk's Python objects
-            P = DDS(A, B, S)
-            done = torch.cuda.Event(); done.record(main)
+            if args.no_fuse:
+                P = DDS(A, B, S)
+                done = torch.cuda.Event(); done.record(main)
             with torch.cuda.stream(down):
                 down.wait_event(done)
                 hP[ch["j0"]:ch["j1"]].copy_(P.pdata, non_blocking=True)
@@ -854,7 +875,8 @@ def run_e2e(args, problem, shard, B_local, dev, rank, world, group):
             "chunks_per_rank": len(chunks), "phases_ms_rank0_last_step": phases,
             "verified": bool(rel <= 1.0 and np.isfinite(rel)),
             "verified_rel_err_over_tolerance": rel,
-            "api": "GMat * GSMat, DDS(GMat, GMat, GSMat), GMat.maddT(GSMat) per column chunk with pinned host operands; "
+            "api": ("GMat * GSMat, DDS(GMat, GMat, GSMat)" if args.no_fuse else "GMat.GSMultDDS(GMat, GSMat)") +
+                   ", GMat.maddT(GSMat) per column chunk with pinned host operands; "
                    "uploads and downloads on their own streams, overlapped with the products"}
 
 

@@ -42,6 +42,7 @@ _SIGNATURES = {
     "bidmat_b200_set_workspace_limit": (_c_int, [ctypes.c_longlong]),
     "bidmat_b200_dsmult_noalloc": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dds_async": (_c_int, [_c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "bidmat_b200_dsmult_dds_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dds0_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_peer_allreduce_sum": (_c_int, [_c_int, _c_int, ctypes.POINTER(ctypes.c_ulonglong),
                                                 ctypes.c_longlong, _c_int, _vp]),

@@ -236,6 +236,26 @@ int bidmat_b200_dds_async(int nrows, int nnz, const float *A, const float *B, co
     return dds_impl<float>(nrows, nnz, A, B, Cir, Cic, P, as_stream(stream));
 }
 
+int bidmat_b200_dsmult_dds_async(int nrows, int ncols, int nnz, const float *A, const float *B, const float *Sdata,
+                                 const int *Sir, const int *Sic, float *C, float *P, bidmat_stream_t stream) {
+    if (nrows < 0 || ncols < 0 || nnz < 0) return (int)cudaErrorInvalidValue;
+    if (nnz == 0 || nrows == 0) return 0;
+    if (!A || !B || !Sdata || !Sir || !Sic || !C || !P) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = as_stream(stream);
+    {
+        const int chunk = pick_chunk(nnz, 32);
+        WorkspaceLease ws(pad256(ga_part_floats(nrows, nnz, chunk) * sizeof(float)) + 256, st);
+        if (ws.err != cudaSuccess) return (int)ws.err;
+        float *part = ws.take<float>(ga_part_floats(nrows, nnz, chunk));
+        cudaError_t err = cudaSuccess;
+        if (launch_as_dds(nrows, nnz, A, B, Sdata, Sir, Sic, C, P, part, chunk, st, &err)) return (int)err;
+    }
+    // shapes the fused kernel does not cover: the two operations one after the other
+    const int e = dsmult_impl<float>(nrows, ncols, nnz, A, Sdata, Sir, Sic, C, st);
+    if (e != 0) return e;
+    return dds_impl<float>(nrows, nnz, A, B, Sir, Sic, P, st);
+}
+
 int bidmat_b200_dds0_async(int nrows, int ncols, int nnz, const float *A, const float *B,
                            const int *Cir, const int *Cjc, float *P, bidmat_stream_t stream) {
     return dds0_impl<float>(nrows, ncols, nnz, A, B, Cir, Cjc, P, as_stream(stream));

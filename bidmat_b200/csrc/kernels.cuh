@@ -526,6 +526,186 @@ dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
 }
 
 // ---------------------------------------------------------------------------
+// A*S and DDS(A,B,S) in one pass (k = 128 or 256 or 512, 16-byte aligned operands):
+//     C[:, ic[j]] += val[j] * A[:, ir[j]]       and       P[j] += <A[:, ir[j]], B[:, ic[j]]>
+// Both operations gather the same column of A for the same nonzero, and that gather
+// (1 KB at k = 256, from L2 for most nonzeros) is what bounds either of them: done
+// together it is paid once.  The kernel is ga_chunk_fast_kernel (runs of equal column,
+// pieces of runs that cross a chunk boundary to `part`, ga_fixup_kernel afterwards)
+// with the sampled product of dds_chunk_fast_kernel added on the gathered column: the
+// column of B is reloaded when the run changes, eight dot products are reduced
+// together, 32 results leave as one coalesced store.  No float atomics.
+// ---------------------------------------------------------------------------
+// Unlike ga_chunk_fast_kernel, the output column of a run is read when the run is flushed, not
+// when it starts: columns of S are long runs, so that read is exposed once per ~100 nonzeros,
+// and the registers it would occupy meanwhile are what lets five CTAs of this kernel share an
+// SM (measured at k = 256: 9.6 ms against 12.9 ms with the early read and four CTAs).
+template <int NT, int U, int TPB, int MINB>
+__global__ void __launch_bounds__(TPB, MINB)
+as_dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
+                         const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ val,
+                         const int *__restrict__ ir, const int *__restrict__ ic,
+                         float *__restrict__ C, float *__restrict__ part, float *__restrict__ P) {
+    constexpr int LPV = 32;
+    constexpr int K = 4 * LPV * NT;
+    constexpr int WPB = TPB / LPV;
+    constexpr int G = LPV / U;
+    static_assert(LPV % U == 0 && 8 % U == 0, "U must divide 8");
+    __shared__ int4 meta[WPB][2][LPV];     // {row, value bits, column, unused}
+
+    const int lane = threadIdx.x & 31;
+    const int w = threadIdx.x >> 5;
+    const unsigned mask = 0xffffffffu;
+    const long long c = (long long)blockIdx.x * WPB + w;
+    if (c >= nchunks) return;
+    const long long j0 = c * (long long)chunk;
+    if (j0 >= nnz) return;
+    const long long j1 = (j0 + chunk < nnz) ? j0 + chunk : nnz;
+    const int nb = (int)((j1 - j0 + LPV - 1) / LPV);
+    const float *Al = A + lane * 4;
+    const float *Bl = B + lane * 4;
+
+    auto stage = [&](int buf, long long base) {
+        const long long jj = base + lane;
+        int4 *dst = &meta[w][buf][lane];
+        if (jj < j1) {
+            cp_async4(&dst->x, ir + jj);
+            cp_async4(&dst->y, val + jj);
+            cp_async4(&dst->z, ic + jj);
+        } else {
+            // padding of the last batch: repeat the last nonzero with value 0 (its dot product is dropped)
+            *dst = make_int4(__ldg(ir + j1 - 1), 0, __ldg(ic + j1 - 1), 0);
+        }
+        cp_async_commit();
+    };
+
+    int cur = __ldg(ic + j0);
+    const int seg_before = (j0 > 0) ? __ldg(ic + j0 - 1) : ~cur;
+    const int seg_after = (j1 < nnz) ? __ldg(ic + j1) : 0;
+    bool head_open = (j0 > 0) && (seg_before == cur);
+    float4 acc[NT], bv[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    // at the start of a run: the column of B its dot products need
+    auto start_run = [&]() {
+        const float4 *bp = reinterpret_cast<const float4 *>(Bl + (size_t)cur * K);
+#pragma unroll
+        for (int t = 0; t < NT; t++) bv[t] = __ldg(bp + t * LPV);
+    };
+    auto flush = [&](bool tail_open) {
+        if (!head_open && !tail_open) {
+            float4 *o = reinterpret_cast<float4 *>(C + (size_t)cur * K) + lane;
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+                float4 old = o[t * LPV];
+                old.x += acc[t].x; old.y += acc[t].y; old.z += acc[t].z; old.w += acc[t].w;
+                o[t * LPV] = old;
+            }
+        } else {
+            float4 *p = reinterpret_cast<float4 *>(part + ((size_t)c * 2 + (head_open ? 0 : 1)) * K) + lane;
+#pragma unroll
+            for (int t = 0; t < NT; t++) p[t * LPV] = acc[t];
+        }
+    };
+
+    stage(0, j0);
+    start_run();
+    for (int b = 0; b < nb; b++) {
+        const long long base = j0 + (long long)b * LPV;
+        if (b + 1 < nb) {
+            stage((b + 1) & 1, base + LPV);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp(mask);
+        const int4 *mt = meta[w][b & 1];
+        // my own result slot of this batch; start its read-modify-write early
+        const int myslot = (lane & 3) * 8 + (lane >> 2);
+        const long long myj = base + myslot;
+        float old = 0.f;
+        if (myj < j1) old = P[myj];
+        float mine = 0.f;
+
+        float4 x[2][U][NT];
+        int4 e[2][U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            e[0][u] = mt[u];
+            const float4 *a = reinterpret_cast<const float4 *>(Al + (size_t)e[0][u].x * K);
+#pragma unroll
+            for (int t = 0; t < NT; t++) x[0][u][t] = __ldg(a + t * LPV);
+        }
+        float p[8];
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            if (g + 1 < G) {
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    e[(g + 1) & 1][u] = mt[(g + 1) * U + u];
+                    const float4 *a = reinterpret_cast<const float4 *>(Al + (size_t)e[(g + 1) & 1][u].x * K);
+#pragma unroll
+                    for (int t = 0; t < NT; t++) x[(g + 1) & 1][u][t] = __ldg(a + t * LPV);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int4 m = e[g & 1][u];
+                if (m.z != cur) {
+                    flush(false);
+                    cur = m.z;
+                    head_open = false;
+                    start_run();
+#pragma unroll
+                    for (int t = 0; t < NT; t++) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                const float v = __int_as_float(m.y);
+                float s = 0.f;
+#pragma unroll
+                for (int t = 0; t < NT; t++) {
+                    const float4 xv = x[g & 1][u][t];
+                    acc[t].x = fmaf(v, xv.x, acc[t].x); acc[t].y = fmaf(v, xv.y, acc[t].y);
+                    acc[t].z = fmaf(v, xv.z, acc[t].z); acc[t].w = fmaf(v, xv.w, acc[t].w);
+                    s = fmaf(xv.x, bv[t].x, s); s = fmaf(xv.y, bv[t].y, s);
+                    s = fmaf(xv.z, bv[t].z, s); s = fmaf(xv.w, bv[t].w, s);
+                }
+                const int pos = g * U + u;             // position in the batch (compile-time: loops are unrolled)
+                p[pos & 7] = s;
+                if ((pos & 7) == 7) {
+                    // reduce the 8 partial dot products of nonzeros pos-7 .. pos
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float give = (lane & 16) ? p[i] : p[i + 4];
+                        const float keep = (lane & 16) ? p[i + 4] : p[i];
+                        p[i] = keep + __shfl_xor_sync(mask, give, 16);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const float give = (lane & 8) ? p[i] : p[i + 2];
+                        const float keep = (lane & 8) ? p[i + 2] : p[i];
+                        p[i] = keep + __shfl_xor_sync(mask, give, 8);
+                    }
+                    {
+                        const float give = (lane & 4) ? p[0] : p[1];
+                        const float keep = (lane & 4) ? p[1] : p[0];
+                        p[0] = keep + __shfl_xor_sync(mask, give, 4);
+                    }
+                    p[0] += __shfl_xor_sync(mask, p[0], 2);
+                    p[0] += __shfl_xor_sync(mask, p[0], 1);
+                    // lane l now holds the dot product of nonzero (l >> 2) of this group of 8
+                    if ((lane & 3) == (pos >> 3)) mine = p[0];
+                }
+            }
+        }
+        if (myj < j1) P[myj] = old + mine;
+        __syncwarp(mask);
+    }
+    const bool tail_open = (j1 < nnz) && (seg_after == cur);
+    flush(tail_open);
+}
+
+// ---------------------------------------------------------------------------
 // Sampled dense-dense product:  P[j] (+)= <A[:, ir[j]], B[:, ic[j]]>
 //
 // One worker per chunk of nonzeros.  The B column is kept in registers while

@@ -42,15 +42,11 @@ cudaError_t launch_ga(int k, long long nnz, const S *D, const S *val, const int 
 #define CALL_FAST(LPV, NT, U, MINB)                                                                    \
     ga_chunk_fast_kernel<LPV, NT, U, kFastThreads, MINB><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, D, val, \
                                                                                         gidx, seg, O, part, range, segmask)
-            // Last argument: minimum CTAs per SM given to the compiler, 0 = leave it to the
-            // compiler (an explicit 1 makes it take 255 registers and halves the occupancy).
-            // k = 256: five CTAs of 128 threads (<= 96 registers) measured 10 % faster than
-            // the default; at k = 128 the cap costs more in spills than the fifth CTA gains.
-            if (s.lpv == 8) CALL_FAST(8, 1, 4, 0);
-            else if (s.lpv == 16) CALL_FAST(16, 1, 4, 0);
-            else if (s.nt == 1) CALL_FAST(32, 1, 4, 0);
-            else if (s.nt == 2) CALL_FAST(32, 2, 2, 5);
-            else CALL_FAST(32, 4, 1, 0);
+            if (s.lpv == 8) { CALL_FAST(8, 1, 4, 0); }
+            else if (s.lpv == 16) { CALL_FAST(16, 1, 4, 0); }
+            else if (s.nt == 1) { CALL_FAST(32, 1, 4, 0); }
+            else if (s.nt == 2) { CALL_FAST(32, 2, 2, 5); }
+            else { CALL_FAST(32, 4, 1, 0); }
 #undef CALL_FAST
             done = true;
         }
@@ -107,6 +103,34 @@ cudaError_t launch_dds(int k, long long nnz, const S *A, const S *B, const int *
     }
     g_launches += 1;
     return cudaGetLastError();
+}
+
+// A*S and DDS in one pass where the fused kernel applies (fp32, k = 128 / 256 / 512, aligned
+// operands); returns false when it does not, and the caller runs the two operations separately.
+inline bool launch_as_dds(int k, long long nnz, const float *A, const float *B, const float *val, const int *ir,
+                          const int *ic, float *C, float *P, float *part, int chunk, cudaStream_t st, cudaError_t *err) {
+    const Shape s = pick_shape(k, is16(A) && is16(B) && is16(C), 4);
+    if (!fast_shape(k, s) || s.lpv != 32 || env_int("BIDMAT_B200_GENERIC", 0) || !env_int("BIDMAT_B200_FUSE_AS_DDS", 1))
+        return false;
+    const long long nchunks = (nnz + chunk - 1) / chunk;
+    const int wpb = kFastThreads / 32;
+    dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
+    {
+        ScopedSpan sp("dsmult_dds_chunk", st);
+        if (s.nt == 1) as_dds_chunk_fast_kernel<1, 4, kFastThreads, 0><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, val, ir, ic, C, part, P);
+        else if (s.nt == 2) as_dds_chunk_fast_kernel<2, 2, kFastThreads, 5><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, val, ir, ic, C, part, P);
+        else as_dds_chunk_fast_kernel<4, 1, kFastThreads, 0><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, val, ir, ic, C, part, P);
+    }
+    if (nchunks > 1) {
+        ScopedSpan sp("ga_fixup", st);
+        dim3 grid(blocks_for(nchunks, 32), 1, 1);
+        if (s.nt == 1) ga_fixup_kernel<float, 4, 32, 1><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, ic, C, part, nullptr, 0xffffffffu, k);
+        else if (s.nt == 2) ga_fixup_kernel<float, 4, 32, 2><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, ic, C, part, nullptr, 0xffffffffu, k);
+        else ga_fixup_kernel<float, 4, 32, 4><<<grid, kThreads, 0, st>>>(k, nnz, chunk, nchunks, ic, C, part, nullptr, 0xffffffffu, k);
+    }
+    g_launches += (nchunks > 1) ? 2 : 1;
+    *err = cudaGetLastError();
+    return true;
 }
 
 // Sorts the nonzero list (ir, ic, v) by key (see rowsort.cuh) in `passes` 8-bit

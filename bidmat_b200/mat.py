@@ -243,6 +243,33 @@ class GMat:
             _finish(err, "GMult: CUDA kernel error in CUMAT.dsmult", st)
         return out
 
+    def GSMultDDS(self, b, s, omatC=None, omatP=None):
+        """(this * s, DDS(this, b, s)) in one pass over s.  BIDMat computes the two with two
+        native calls on the same operands (GMat.GSMult, GMat.scala:1041-1049, and GSMat.DDS,
+        GSMat.scala:649-667); both gather the same columns of `this`, so the library offers them
+        together.  Same checks, outputs and flop count as the two calls."""
+        s = GSMat.of(s, self.t.device)
+        if self.ncols != s.nrows:
+            raise RuntimeError("GSMult dimensions mismatch (%d %d) (%d %d)" % (self.nrows, self.ncols, s.nrows, s.ncols))
+        if self.nrows != b.nrows or s.ncols != b.ncols:
+            raise RuntimeError("dimensions mismatch %d,%d  %d,%d  %d,%d"
+                               % (self.nrows, self.ncols, b.nrows, b.ncols, s.nrows, s.ncols))
+        C = _new_or_check(self.nrows, s.ncols, omatC, self.t.device)
+        C.clear()
+        P = s._like(omatP)
+        P.pir.copy_(s.pir)
+        P.pic.copy_(s.pic)
+        P._plans = s._plans
+        P.pdata.zero_()
+        s._debug_check()
+        Mat.nflops += 4 * self.nrows * s.nnz
+        with torch.cuda.device(self.t.device):
+            st = _stream(self.t.device)
+            err = _L.bidmat_b200_dsmult_dds_async(self.nrows, s.ncols, s.nnz, self.pdata, b.pdata, _ptr(s.pdata),
+                                                  _ptr(s.pir), _ptr(s.pic), C.pdata, _ptr(P.pdata), st.cuda_stream)
+            _finish(err, "GMult: CUDA kernel error in CUMAT.dsmult / CUMAT.dds (one pass)", st)
+        return C, P
+
     # ---- B *^ S ---------------------------------------------------------
     def GSMultT(self, a, oldmat=None):
         """GMat.GSMultT (GMat.scala:1076-1084)."""

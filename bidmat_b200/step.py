@@ -68,8 +68,9 @@ class PathStep:
       * several GPUs, NCCL: NCCL adds whole buffers, so G is cleared every step.
     """
 
-    def __init__(self, k, shard, A, B_local, stream, group=None, peer_reduce=False, use_plan=True):
+    def __init__(self, k, shard, A, B_local, stream, group=None, peer_reduce=False, use_plan=True, fuse=True):
         self.k, self.S, self.A, self.B, self.stream, self.group = int(k), shard, A, B_local, stream, group
+        self.fuse = bool(fuse)      # A*S and DDS in one pass (run()); the separate calls stay available
         dev = A.device
         self.C = torch.zeros((shard.n, k), dtype=torch.float32, device=dev)
         self.P = torch.zeros(shard.nnz, dtype=torch.float32, device=dev)
@@ -153,6 +154,16 @@ class PathStep:
             _ck(_L.bidmat_b200_dds_async(self.k, S.nnz, self.A.data_ptr(), self.B.data_ptr(), S.ir.data_ptr(),
                                          S.ic.data_ptr(), self.P.data_ptr(), self.stream.cuda_stream), "dds")
 
+    def dsmult_dds(self):
+        """C = A*S and P = DDS(A,B,S) in one pass over S (both gather the same columns of A)."""
+        S = self.S
+        with torch.cuda.stream(self.stream):
+            self.C.zero_()
+            self.P.zero_()
+            _ck(_L.bidmat_b200_dsmult_dds_async(self.k, S.n, S.nnz, self.A.data_ptr(), self.B.data_ptr(),
+                                                S.data.data_ptr(), S.ir.data_ptr(), S.ic.data_ptr(), self.C.data_ptr(),
+                                                self.P.data_ptr(), self.stream.cuda_stream), "dsmult_dds")
+
     def dsmultT_local(self, data=None):
         """This rank's partial of B*^S over its column shard (no communication).
         `data`: other values on the same structure (e.g. a DDS result), default S's own."""
@@ -219,8 +230,11 @@ class PathStep:
         A*S and DDS; the step ends when the reduced G is complete."""
         self.dsmultT_local()
         work = self.allreduce_start()
-        self.dsmult()
-        self.dds()
+        if self.fuse:
+            self.dsmult_dds()
+        else:
+            self.dsmult()
+            self.dds()
         self.wait(work)
 
     def close(self):

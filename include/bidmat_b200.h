@@ -105,6 +105,20 @@ BIDMAT_B200_API int bidmat_b200_dds_async(int nrows, int nnz, const float *A, co
 BIDMAT_B200_API int bidmat_b200_dds0_async(int nrows, int ncols, int nnz, const float *A, const float *B,
                            const int *Cir, const int *Cjc, float *P, bidmat_stream_t stream);
 
+/* A*S and DDS(A,B,S) on the same sparse matrix in one pass:
+ *     C(nrows x ncols) += A(nrows x m) * S          and          P[j] += <A[:, Sir[j]], B[:, Sic[j]]>
+ * with S = (Sdata, Sir, Sic).  Same results as bidmat_b200_dsmult_async followed by
+ * bidmat_b200_dds_async (each output is computed by the same arithmetic as in the separate
+ * kernels).  Both operations gather the same column of A for every nonzero and that gather bounds
+ * either of them; for fp32 operands with nrows in {128, 256, 512} and 16-byte aligned pointers one
+ * kernel does it once for both, other shapes run the two operations one after the other.
+ * Stream-ordered.  No counterpart in the reference's native interface: there the two are separate
+ * calls (CUMAT.dsmult, CUMAT.dds: CUMAT.java:143,211), made one after the other on the same
+ * operands by factorisation loops (P = DDS(A,B,S); C = A*S). */
+BIDMAT_B200_API int bidmat_b200_dsmult_dds_async(int nrows, int ncols, int nnz, const float *A, const float *B,
+                                                 const float *Sdata, const int *Sir, const int *Sic, float *C,
+                                                 float *P, bidmat_stream_t stream);
+
 /* Double-precision twins of the four operations (BIDMat's GDMat / GSDMat path).
  * Same semantics as the fp32 functions above; dense operands and values are fp64.
  * Replaces: dsmult / dsmultT / dds / dds0 on doubles (jni/include/MatKernelD.hpp:43,49,53,55,

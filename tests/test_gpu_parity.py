@@ -344,3 +344,50 @@ def test_generic_kernels_at_the_fast_path_heights(cuda_device, k, monkeypatch):
     m, n = 120, 80
     jc, ir, data = random_csc(m, n, 0.25, rng, empty_cols=(5,))
     check_all_ops(k, m, n, jc, ir, data, cuda_device, rng)
+
+
+@pytest.mark.parametrize("chunk", [0, 32])
+@pytest.mark.parametrize("k", [12, 64, 128, 256, 512, 516])
+def test_product_and_sampled_product_in_one_pass(cuda_device, k, chunk, monkeypatch):
+    """bidmat_b200_dsmult_dds_async: same results as dsmult followed by dds (bit for bit: the
+    same arithmetic per output), against the CPU checker, accumulating into non-zero outputs;
+    k = 128 / 256 / 512 take the one-pass kernel, the others the two operations in sequence."""
+    from gpu_util import L
+    if chunk:
+        monkeypatch.setenv("BIDMAT_B200_CHUNK", str(chunk))
+    rng = np.random.default_rng(900 + k + chunk)
+    m, n = 170, 120
+    jc, ir, data = random_csc(m, n, 0.25, rng, empty_cols=(0, 7, 119))
+    S = DeviceCSC(m, n, jc, ir, data, cuda_device)
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((n, k)).astype(np.float32)
+    C0 = rng.standard_normal((n, k)).astype(np.float32)
+    P0 = rng.standard_normal(S.nnz).astype(np.float32)
+    dA, dB = dev(A, cuda_device), dev(B, cuda_device)
+    C, P = dev(C0, cuda_device), dev(P0, cuda_device)
+    err = L.bidmat_b200_dsmult_dds_async(k, n, S.nnz, dA.data_ptr(), dB.data_ptr(), S.data.data_ptr(), S.ir.data_ptr(),
+                                         S.ic.data_ptr(), C.data_ptr(), P.data_ptr(), None)
+    assert err == 0
+    torch.cuda.synchronize()
+    _, Cabs = oracle.dsmult_f64(A, data, ir, jc)
+    _, Pabs = oracle.dds_f64(A, B, ir, jc)
+    assert_close_scaled(C.cpu().numpy(), oracle.dsmult(A, data, ir, jc, out=C0.copy()), Cabs + np.abs(C0), RTOL_DSMULT, "one pass: A*S")
+    assert_close_scaled(P.cpu().numpy(), oracle.dds(A, B, ir, jc) + P0, Pabs + np.abs(P0), RTOL_DDS, "one pass: DDS")
+    C2 = abi_dsmult(dA, S, dev(C0, cuda_device))
+    P2 = abi_dds(dA, dB, S, dev(P0, cuda_device))
+    assert torch.equal(C.view(torch.int32), C2.view(torch.int32))
+    assert_close_scaled(P.cpu().numpy(), P2.cpu().numpy(), Pabs + np.abs(P0), RTOL_DDS, "one pass vs separate DDS")
+
+
+def test_mirror_product_and_sampled_product_in_one_pass(cuda_device):
+    from bidmat_b200.mat import DDS, GMat, GSMat, SMat
+    rng = np.random.default_rng(77)
+    k, m, n = 256, 90, 60
+    jc, ir, data = random_csc(m, n, 0.2, rng)
+    S = GSMat.fromSMat(SMat(m, n, jc, ir, data), cuda_device)
+    A = GMat.from_numpy(rng.standard_normal((m, k)).astype(np.float32), cuda_device)
+    B = GMat.from_numpy(rng.standard_normal((n, k)).astype(np.float32), cuda_device)
+    C, P = A.GSMultDDS(B, S)
+    assert torch.equal(C.t, (A * S).t)
+    assert torch.equal(P.pir, S.pir) and torch.equal(P.pic, S.pic)
+    assert torch.allclose(P.pdata, DDS(A, B, S).pdata, rtol=1e-5, atol=1e-5)
