@@ -430,6 +430,15 @@ def run_b200(args, rank, local_rank, world):
     if not args.no_verify and not args.emulate_shard:
         verified = verify_step(st, problem, shard, B_local, world, dev)
 
+    # the sum of the partials alone, with nothing running beside it (several GPUs; after the check above,
+    # the buffers then hold sums of sums)
+    sum_alone_ms = None
+    if world > 1 and not args.emulate_shard:
+        with torch.cuda.stream(stream):
+            def sum_only():
+                st.wait(st.allreduce_start())
+            sum_alone_ms = time_calls(sum_only, stream, 3, 1)
+
     # max over ranks
     red = torch.tensor([total_ms] + [op_ms[o] for o in ops], dtype=torch.float64, device=dev)
     nnz_all = torch.tensor([shard.nnz], dtype=torch.float64, device=dev)
@@ -449,6 +458,7 @@ def run_b200(args, rank, local_rank, world):
                        "library kernel over NVLink peer memory, touched rows only" if st.touched is not None
                        else "library kernel over NVLink peer memory") if st.peer is not None else "NCCL")
 
+    st_parts = st.parts
     extras = None
     if rank == 0 and world == 1 and not args.no_extras and not args.emulate_shard:
         extras = run_extras(args, problem, shard, B_local, st, dev, stream)
@@ -534,7 +544,8 @@ def run_b200(args, rank, local_rank, world):
                                                                 if overwrite else "G cleared every step"))}),
         "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline, "e2e": e2e, "verified": verified,
         "allreduce_exposed_ms": op_ms_max["allreduce_exposed"] if world > 1 else 0.0,
-        "allreduce": allreduce_kind,
+        "allreduce": allreduce_kind, "allreduce_alone_ms_rank0": sum_alone_ms,
+        "dsmultT_row_parts": (len(st_parts) - 1) if st_parts else None,
         "touched_row_fraction_mean_over_ranks": float(touched[0]) / world if plan_info else None,
         "plan": plan_info,
     }

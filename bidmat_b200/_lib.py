@@ -50,6 +50,11 @@ _SIGNATURES = {
                                                      ctypes.c_longlong, _vp, _c_int, _vp]),
     "bidmat_b200_mc_allreduce_sum": (_c_int, [_c_int, _c_int, _vp, ctypes.c_longlong, _c_int, _vp]),
     "bidmat_b200_plan_clear_untouched": (_c_int, [_vp, _c_int, _vp, _vp]),
+    "bidmat_b200_peer_allreduce_sum_rows_range": (_c_int, [_c_int, _c_int, ctypes.POINTER(ctypes.c_ulonglong), _c_int,
+                                                           ctypes.c_longlong, _vp, ctypes.c_longlong, ctypes.c_longlong,
+                                                           _c_int, _vp]),
+    "bidmat_b200_plan_row_parts": (_c_int, [_vp, _c_int, ctypes.POINTER(_c_int)]),
+    "bidmat_b200_dsmultT_planned_part": (_c_int, [_vp, _c_int, _c_int, _c_int, _vp, _vp, _vp, _c_int, _c_int, _vp]),
     "bidmat_b200_expand_jc": (_c_int, [_c_int, _c_int, _vp, _vp, _vp]),
     "bidmat_b200_compress_ic": (_c_int, [_c_int, _c_int, _vp, _vp, _vp]),
     "bidmat_b200_transpose_csc": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

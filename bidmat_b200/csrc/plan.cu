@@ -38,6 +38,10 @@ struct bidmat_b200_plan {
     void *part = nullptr;          // slots of the split runs, nslots * k elements
     int *mismatch = nullptr;       // result of plan_verify
     std::vector<int> block_c0, block_nch;
+    // host copies for running a single-block plan in row ranges (bidmat_b200_plan_row_parts)
+    std::vector<int> h_chunk_row;      // row of the first nonzero of a chunk, -1 when the chunk starts inside a row
+    std::vector<int> h_group_row, h_group_run0;
+    std::vector<int> part_chunk, part_run, part_group, part_row;   // bounds per part, nparts + 1 entries each
     int nchunks = 0, nruns = 0, ngroups = 0, nslots = 0, nclear = 0;
     long long touched_rows = 0;
     long long row_runs = 0;        // runs of equal (column block, row): each one updates its output column once
@@ -213,6 +217,7 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
                 d.w = tail ? -2 : -1;
             }
             h_desc[(size_t)p->block_c0[b] + c] = d;
+            p->h_chunk_row.push_back(head ? -1 : (int)(h_kfirst[e] & lay.rowmask));
         }
     }
     p->nslots = slot;
@@ -229,6 +234,9 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
         h_groups.back().z++;
     }
     p->ngroups = (int)h_groups.size();
+    p->h_group_row.resize(h_groups.size());
+    p->h_group_run0.resize(h_groups.size());
+    for (size_t g = 0; g < h_groups.size(); g++) { p->h_group_row[g] = h_groups[g].x; p->h_group_run0[g] = h_groups[g].y; }
     p->nclear = (int)h_clear.size();
     for (int r = 0; r < m; r++) p->touched_rows += (h_first[r] != kNoBlock);
 
@@ -269,10 +277,14 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
     return 0;
 }
 
+// part < 0: the whole product.  part >= 0: only the row range `part` of a single-block plan
+// (bidmat_b200_plan_row_parts): its chunks, then the fix-up of the split rows inside it.
 template <typename S>
 int plan_run(bidmat_b200_plan *p, int k, int ncols, int nnz, const S *A, const S *Bdata, S *C, int flags,
-             cudaStream_t st) {
+             cudaStream_t st, int part_index = -1) {
     if (!plan_ok(p)) return (int)cudaErrorInvalidValue;
+    if (part_index >= 0 && (p->part_chunk.empty() || part_index + 1 >= (int)p->part_chunk.size()))
+        return (int)cudaErrorInvalidValue;
     if (p->elem != (int)sizeof(S) || k != p->k || ncols != p->ncols || nnz != p->nnz) return (int)cudaErrorInvalidValue;
     if (!A || !Bdata || !C) return (int)cudaErrorInvalidValue;
     if (flags & ~BIDMAT_B200_PLAN_OVERWRITE) return (int)cudaErrorInvalidValue;
@@ -290,6 +302,7 @@ int plan_run(bidmat_b200_plan *p, int k, int ncols, int nnz, const S *A, const S
     bool fast = false;
     if constexpr (std::is_same<S, float>::value) fast = fast_shape(k, s) && !env_int("BIDMAT_B200_GENERIC", 0);
     const bool fused = fast && env_int("BIDMAT_B200_PLAN_FUSED", 1) != 0;
+    if (part_index >= 0 && !fused) return (int)cudaErrorNotSupported;   // parts need the kernel that reads the values in place
     WorkspaceLease ws(fused ? 256 : pad256(n * sizeof(S)) + 256, st);
     if (ws.err != cudaSuccess) return (int)ws.err;
     S *vals = fused ? nullptr : ws.take<S>(n);
@@ -299,16 +312,20 @@ int plan_run(bidmat_b200_plan *p, int k, int ncols, int nnz, const S *A, const S
         else plan_permute_kernel<S><<<148 * 16, 256, 0, st>>>((long long)nnz, p->perm, Bdata, vals);
         g_launches += 1;
     }
-    if (storebit && p->nclear > 0) {
+    if (storebit && p->nclear > 0 && part_index <= 0) {
         plan_clear_rows_kernel<S><<<(unsigned)(((size_t)p->nclear * 32 + 255) / 256), 256, 0, st>>>(k, p->nclear,
                                                                                                    p->clear_rows, C);
         g_launches += 1;
     }
     const bool prefetch = env_int("BIDMAT_B200_PLAN_PREFETCH", 1) != 0;
     for (int b = 0; b < p->lay.nblocks; b++) {
-        const int nch = p->block_nch[b];
-        if (nch == 0) continue;
+        int nch = p->block_nch[b];
         const int4 *desc = p->desc + p->block_c0[b];
+        if (part_index >= 0) {           // single block: the chunks of this row range
+            desc += p->part_chunk[part_index];
+            nch = p->part_chunk[part_index + 1] - p->part_chunk[part_index];
+        }
+        if (nch == 0) continue;
         ScopedSpan sp("dsmultT_ga_chunk", st);
         bool done = false;
         if constexpr (std::is_same<S, float>::value) {
@@ -352,14 +369,19 @@ int plan_run(bidmat_b200_plan *p, int k, int ncols, int nnz, const S *A, const S
         }
         g_launches += 1;
     }
-    if (p->nruns > 0) {
+    int run0 = 0, nruns = p->nruns, group0 = 0, ngroups = p->ngroups;
+    if (part_index >= 0) {
+        run0 = p->part_run[part_index]; nruns = p->part_run[part_index + 1] - run0;
+        group0 = p->part_group[part_index]; ngroups = p->part_group[part_index + 1] - group0;
+    }
+    if (nruns > 0) {
         ScopedSpan sp("ga_fixup", st);
-        dim3 grid(blocks_for(p->nruns, s.lpv), s.tiles, 1);
-        dim3 ggrid(blocks_for(p->ngroups, s.lpv), s.tiles, 1);
+        dim3 grid(blocks_for(nruns, s.lpv), s.tiles, 1);
+        dim3 ggrid(blocks_for(ngroups, s.lpv), s.tiles, 1);
 #define CALL_FIX(VEC, LPV, NT)                                                                              \
     do {                                                                                                    \
-        plan_fixup_runs_kernel<S, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, p->nruns, p->runs, part);     \
-        plan_fixup_rows_kernel<S, VEC, LPV, NT><<<ggrid, kThreads, 0, st>>>(k, p->ngroups, p->groups, p->runs, C, \
+        plan_fixup_runs_kernel<S, VEC, LPV, NT><<<grid, kThreads, 0, st>>>(k, nruns, p->runs + run0, part); \
+        plan_fixup_rows_kernel<S, VEC, LPV, NT><<<ggrid, kThreads, 0, st>>>(k, ngroups, p->groups + group0, p->runs, C, \
                                                                             part, segmask);                 \
     } while (0)
         DISPATCH_SHAPE(s, CALL_FIX);
@@ -386,6 +408,42 @@ int bidmat_b200_dsmultT_planned(bidmat_b200_plan_t plan, int nrows, int ncols, i
 int bidmat_b200_dsmultT_planned_f64(bidmat_b200_plan_t plan, int nrows, int ncols, int nnz, const double *A,
                                     const double *Bdata, double *C, int flags, bidmat_stream_t stream) {
     return plan_run<double>(plan, nrows, ncols, nnz, A, Bdata, C, flags, as_stream(stream));
+}
+
+int bidmat_b200_plan_row_parts(bidmat_b200_plan_t p, int nparts, int *row_bounds) {
+    if (!p || p->magic != kPlanMagic || nparts < 1 || !row_bounds) return (int)cudaErrorInvalidValue;
+    if (p->lay.nblocks != 1 || p->nchunks < nparts) return (int)cudaErrorNotSupported;
+    // Part boundaries at chunks that start a new row (rows ascend through the single block), near
+    // equal chunk counts; the runs and groups of a part are those of its rows (both lists ascend by row).
+    std::vector<int> chunk(1, 0), row(1, 0);
+    for (int i = 1; i < nparts; i++) {
+        int c = (int)((long long)p->nchunks * i / nparts);
+        if (c <= chunk.back()) c = chunk.back() + 1;
+        while (c < p->nchunks && p->h_chunk_row[(size_t)c] < 0) c++;
+        if (c >= p->nchunks) break;
+        chunk.push_back(c);
+        row.push_back(p->h_chunk_row[(size_t)c]);
+    }
+    const int actual = (int)chunk.size();
+    chunk.push_back(p->nchunks);
+    row.push_back(p->m);
+    std::vector<int> grp(1, 0), run(1, 0);
+    for (int i = 1; i <= actual; i++) {
+        const int g = (int)(std::lower_bound(p->h_group_row.begin(), p->h_group_row.end(), row[(size_t)i]) -
+                            p->h_group_row.begin());
+        grp.push_back(g);
+        run.push_back(g < p->ngroups ? p->h_group_run0[(size_t)g] : p->nruns);
+    }
+    p->part_chunk = chunk; p->part_row = row; p->part_group = grp; p->part_run = run;
+    for (int i = 0; i <= actual; i++) row_bounds[i] = row[(size_t)i];
+    for (int i = actual + 1; i <= nparts; i++) row_bounds[i] = p->m;
+    return actual == nparts ? 0 : (int)cudaErrorNotSupported;
+}
+
+int bidmat_b200_dsmultT_planned_part(bidmat_b200_plan_t plan, int nrows, int ncols, int nnz, const float *A,
+                                     const float *Bdata, float *C, int flags, int part, bidmat_stream_t stream) {
+    if (part < 0) return (int)cudaErrorInvalidValue;
+    return plan_run<float>(plan, nrows, ncols, nnz, A, Bdata, C, flags, as_stream(stream), part);
 }
 
 int bidmat_b200_plan_verify(bidmat_b200_plan_t p, int ncols, int nnz, const int *Bir, const int *Bic,

@@ -94,6 +94,23 @@ class PathStep:
                 self.peer = None
         if self.peer is None:
             self.G = torch.zeros((shard.m, k), dtype=torch.float32, device=dev)
+        # A single-block plan (one rank's shard on many GPUs) runs in row ranges, and the sum of a
+        # range starts while the later ranges are still being multiplied.  The ranks agree on the
+        # ranges once: the smallest of their bounds, so a range is complete everywhere when summed.
+        self.parts = None
+        self._pending = None
+        nparts = int(os.environ.get("BIDMAT_B200_PIPE_PARTS", "4"))
+        if self.peer is not None and self.touched is not None and nparts > 1:
+            import ctypes
+            import torch.distributed as dist
+            bounds = (ctypes.c_int * (nparts + 1))()
+            rc = _L.bidmat_b200_plan_row_parts(self.plan.handle, nparts, bounds)
+            t = torch.tensor([0 if rc == 0 else 1] + [int(b) for b in bounds], dtype=torch.int64, device=dev)
+            t[0] = -t[0]                      # MIN over ranks: -1 as soon as one rank cannot
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+            if int(t[0]) == 0:
+                self.parts = [int(v) for v in t[1:]]
+                self.parts[0], self.parts[-1] = 0, shard.m
         # clear G every step?  Not when the plan overwrites and nobody reads the untouched rows.
         self.mc = self.peer is not None and bool(self.peer["mc"])
         self.overwrite = self.plan is not None and (group is None or (self.peer is not None and
@@ -169,6 +186,8 @@ class PathStep:
         `data`: other values on the same structure (e.g. a DDS result), default S's own."""
         S = self.S
         vals = S.data if data is None else data
+        if self.parts is not None:
+            return self._dsmultT_in_parts(vals)
         with torch.cuda.stream(self.stream):
             if not self.overwrite:
                 self.G.zero_()   # GMat.GSMultT clears the output (GMat.scala:1082)
@@ -186,11 +205,39 @@ class PathStep:
                                                  S.ir.data_ptr(), S.ic.data_ptr(), self.G.data_ptr(), S.m,
                                                  self.stream.cuda_stream), "dsmultT")
 
+    def _dsmultT_in_parts(self, vals):
+        """B*^S range of rows after range of rows; the sum over the ranks of a range is queued
+        on the side stream as soon as the range is done here (and, by the rank synchronisation
+        in front of it, everywhere)."""
+        import torch.distributed as dist
+        S, pr = self.S, self.peer
+        nparts = len(self.parts) - 1
+        for r in range(nparts):
+            with torch.cuda.stream(self.stream):
+                _ck(_L.bidmat_b200_dsmultT_planned_part(self.plan.handle, self.k, S.n, S.nnz, self.B.data_ptr(),
+                                                        vals.data_ptr(), self.G.data_ptr(), 1, r,
+                                                        self.stream.cuda_stream), "dsmultT (planned, part)")
+                done = torch.cuda.Event()
+                done.record(self.stream)
+            with torch.cuda.stream(pr["comm"]):
+                pr["comm"].wait_event(done)
+                before = dist.all_reduce(pr["flag"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+                before.wait()
+                _ck(_L.bidmat_b200_peer_allreduce_sum_rows_range(pr["world"], pr["rank"], pr["addrs"], self.k, S.m,
+                                                                 self.touched.data_ptr(), self.parts[r],
+                                                                 self.parts[r + 1], pr["ctas"], pr["comm"].cuda_stream),
+                    "peer_allreduce_sum_rows_range")
+        with torch.cuda.stream(pr["comm"]):
+            self._pending = dist.all_reduce(pr["flag"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+
     def allreduce_start(self):
         """Starts the sum of the partials over ranks off the caller's stream, which
         is free to run A*S and DDS meanwhile; returns what to wait on."""
         if self.group is None:
             return None
+        if self._pending is not None:         # the sums were queued range by range with the product
+            work, self._pending = self._pending, None
+            return work
         import torch.distributed as dist
         with torch.cuda.stream(self.stream):
             if self.peer is None:

@@ -189,6 +189,19 @@ BIDMAT_B200_API int bidmat_b200_plan_info(bidmat_b200_plan_t plan, long long *ou
  * nonzero: bit r%32 of word r/32 is set for such a row r.  Stream-ordered. */
 BIDMAT_B200_API int bidmat_b200_plan_touched_rows(bidmat_b200_plan_t plan, unsigned *bitmap,
                                                   bidmat_stream_t stream);
+/* A plan with a single column block (the dense operand fits the L2 rule: small problems, or one
+ * rank's shard on many GPUs) can be run in `nparts` consecutive ROW RANGES of the result:
+ * plan_row_parts fixes the ranges (row_bounds[0..nparts], ascending, 0 and m at the ends) and
+ * planned_part computes the columns of C in range `part` completely (its chunks, then the fix-up of
+ * the split rows inside it).  Calling the parts 0 .. nparts-1 in order on one stream gives what
+ * bidmat_b200_dsmultT_planned gives; a consumer of the first rows (the sum over the ranks) can
+ * start while the later parts still run.  cudaErrorNotSupported (801): several column blocks, a
+ * shape other than fp32 with nrows in {32 .. 512} and aligned pointers, or fewer chunks than parts. */
+BIDMAT_B200_API int bidmat_b200_plan_row_parts(bidmat_b200_plan_t plan, int nparts, int *row_bounds);
+BIDMAT_B200_API int bidmat_b200_dsmultT_planned_part(bidmat_b200_plan_t plan, int nrows, int ncols, int nnz,
+                                                     const float *A, const float *Bdata, float *C, int flags,
+                                                     int part, bidmat_stream_t stream);
+
 /* Zeroes the columns of C (nrows x m, of the plan's element type) that no nonzero of S names: with
  * BIDMAT_B200_PLAN_OVERWRITE before it, C then equals the product everywhere without a full clear
  * (what a sum over whole buffers, e.g. bidmat_b200_mc_allreduce_sum, needs).  Stream-ordered. */
@@ -253,6 +266,12 @@ BIDMAT_B200_API int bidmat_b200_peer_allreduce_sum_rows(int world, int rank,
                                                         const unsigned long long *peer_addresses, int k,
                                                         long long m, const unsigned *touched, int ctas,
                                                         bidmat_stream_t stream);
+/* The same for the columns [row_begin, row_end) only (a row range of a plan run in parts). */
+BIDMAT_B200_API int bidmat_b200_peer_allreduce_sum_rows_range(int world, int rank,
+                                                              const unsigned long long *peer_addresses, int k,
+                                                              long long m, const unsigned *touched,
+                                                              long long row_begin, long long row_end, int ctas,
+                                                              bidmat_stream_t stream);
 
 /* The same sum through the NVSwitch, for buffers that are bound to a multicast object:
  * multicast_address is the multicast mapping of the ranks' buffers of `count` floats (count a
