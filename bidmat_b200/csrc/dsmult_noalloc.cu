@@ -96,7 +96,7 @@ extern "C" int bidmat_b200_dsmult_noalloc(int nrows, int ncols, int nnz, const f
         const int wpb = kFast / s.lpv;
         dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
 #define CALL_FAST_NOALLOC(LPV, NT, U, MINB)                                                             \
-    ga_chunk_fast_kernel<LPV, NT, U, kFast, MINB><<<fgrid, kFast, 0, st>>>(nnz, ichunk, nchunks, A, Bdata, Bir, Bic, C, \
+    ga_chunk_fast_kernel<float, LPV, NT, U, kFast, MINB><<<fgrid, kFast, 0, st>>>(nnz, ichunk, nchunks, A, Bdata, Bir, Bic, C, \
                                                                         part, nullptr, 0xffffffffu)
         if (s.lpv == 8) CALL_FAST_NOALLOC(8, 1, 4, 0);
         else if (s.lpv == 16) CALL_FAST_NOALLOC(16, 1, 4, 0);

@@ -234,9 +234,10 @@ ga_fixup_kernel(int k, long long nnz, int chunk, long long nchunks,
 }
 
 // ---------------------------------------------------------------------------
-// Fast paths for the common dense heights k = 4*LPV*NT (32, 64, 128, 256, 512)
-// with 16-byte aligned operands: every lane owns exactly NT float4 of a
-// column, so no bounds predicates are needed.
+// Fast paths for the common dense heights k = VEC*LPV*NT (fp32: 32, 64, 128, 256,
+// 512; fp64: 16, 32, 64, 128, 256) with 16-byte aligned operands: every lane owns
+// exactly NT 16-byte vectors (float4 / double2) of a column, so no bounds
+// predicates are needed.
 //
 // The (index, value, segment) triples of the next LPV nonzeros are staged in
 // shared memory with cp.async while the current LPV are processed, so the
@@ -249,6 +250,10 @@ __device__ __forceinline__ void cp_async4(void *smem_dst, const void *gmem_src) 
     const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(gmem_src) : "memory");
 }
+__device__ __forceinline__ void cp_async8(void *smem_dst, const void *gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
@@ -258,18 +263,61 @@ template <int LPV> __device__ __forceinline__ void worker_sync(unsigned mask) {
     __syncwarp(mask);
 }
 
-template <int LPV, int NT, int U, int TPB, int MINB = 0>
+// What the predicate-free kernels need to know about the scalar type: the 16-byte
+// vector a lane loads, its arithmetic, and where the fields of a staged nonzero
+// sit in its 16-byte shared-memory record.
+//   float : {gather index, value bits, segment, source position}
+//   double: {gather index, segment, value low word, value high word}
+template <typename S> struct FastOps;
+template <> struct FastOps<float> {
+    typedef float4 vec;
+    static constexpr int VEC = 4;
+    static __device__ __forceinline__ vec zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+    static __device__ __forceinline__ void axpy(float v, const vec &x, vec &a) {
+        a.x = fmaf(v, x.x, a.x); a.y = fmaf(v, x.y, a.y); a.z = fmaf(v, x.z, a.z); a.w = fmaf(v, x.w, a.w);
+    }
+    static __device__ __forceinline__ void add(vec &o, const vec &a) { o.x += a.x; o.y += a.y; o.z += a.z; o.w += a.w; }
+    static __device__ __forceinline__ float dot(const vec &x, const vec &b, float s) {
+        s = fmaf(x.x, b.x, s); s = fmaf(x.y, b.y, s); s = fmaf(x.z, b.z, s); s = fmaf(x.w, b.w, s);
+        return s;
+    }
+    static __device__ __forceinline__ int seg(const int4 &m) { return m.z; }
+    static __device__ __forceinline__ float val(const int4 &m) { return __int_as_float(m.y); }
+    static __device__ __forceinline__ void stage_seg(int4 *dst, const int *src) { cp_async4(&dst->z, src); }
+    static __device__ __forceinline__ void stage_val(int4 *dst, const float *src) { cp_async4(&dst->y, src); }
+    static __device__ __forceinline__ int4 pad(int gidx, int sg) { return make_int4(gidx, 0, sg, -1); }   // value 0
+};
+template <> struct FastOps<double> {
+    typedef double2 vec;
+    static constexpr int VEC = 2;
+    static __device__ __forceinline__ vec zero() { return make_double2(0.0, 0.0); }
+    static __device__ __forceinline__ void axpy(double v, const vec &x, vec &a) { a.x = fma(v, x.x, a.x); a.y = fma(v, x.y, a.y); }
+    static __device__ __forceinline__ void add(vec &o, const vec &a) { o.x += a.x; o.y += a.y; }
+    static __device__ __forceinline__ double dot(const vec &x, const vec &b, double s) {
+        s = fma(x.x, b.x, s); s = fma(x.y, b.y, s);
+        return s;
+    }
+    static __device__ __forceinline__ int seg(const int4 &m) { return m.y; }
+    static __device__ __forceinline__ double val(const int4 &m) { return __hiloint2double(m.w, m.z); }
+    static __device__ __forceinline__ void stage_seg(int4 *dst, const int *src) { cp_async4(&dst->y, src); }
+    static __device__ __forceinline__ void stage_val(int4 *dst, const double *src) { cp_async8(&dst->z, src); }
+    static __device__ __forceinline__ int4 pad(int gidx, int sg) { return make_int4(gidx, sg, 0, 0); }    // value 0.0
+};
+
+template <typename S, int LPV, int NT, int U, int TPB, int MINB = 0>
 __global__ void __launch_bounds__(TPB, MINB)
 ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
-                     const float *__restrict__ D, const float *__restrict__ val,
+                     const S *__restrict__ D, const S *__restrict__ val,
                      const int *__restrict__ gidx, const int *__restrict__ seg,
-                     float *__restrict__ O, float *__restrict__ part,
+                     S *__restrict__ O, S *__restrict__ part,
                      const int *__restrict__ range, unsigned segmask) {
-    constexpr int K = 4 * LPV * NT;        // dense height handled by this instantiation
+    typedef FastOps<S> F;
+    typedef typename F::vec vec;
+    constexpr int K = F::VEC * LPV * NT;   // dense height handled by this instantiation
     constexpr int WPB = TPB / LPV;         // workers per CTA
     constexpr int G = LPV / U;             // groups of U nonzeros per staged batch
     static_assert(LPV % U == 0, "U must divide LPV");
-    __shared__ int4 meta[WPB][2][LPV];     // {gather index, value bits, segment, unused}
+    __shared__ int4 meta[WPB][2][LPV];     // staged nonzeros, fields as FastOps<S> lays them out
 
     const int lane = threadIdx.x & (LPV - 1);
     const int w = threadIdx.x / LPV;
@@ -283,18 +331,18 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     if (j0 >= hi) return;
     const long long j1 = (j0 + chunk < hi) ? j0 + chunk : hi;
     const int nb = (int)((j1 - j0 + LPV - 1) / LPV);
-    const float *Dl = D + lane * 4;        // this lane's first float4 inside any column
+    const S *Dl = D + lane * F::VEC;       // this lane's first 16-byte vector inside any column
 
     auto stage = [&](int buf, long long base) {
         const long long jj = base + lane;
         int4 *dst = &meta[w][buf][lane];
         if (jj < j1) {
             cp_async4(&dst->x, gidx + jj);
-            cp_async4(&dst->y, val + jj);
-            cp_async4(&dst->z, seg + jj);
+            F::stage_val(dst, val + jj);
+            F::stage_seg(dst, seg + jj);
         } else {
             // padding of the last batch: repeat the last nonzero with value 0
-            *dst = make_int4(__ldg(gidx + j1 - 1), 0, __ldg(seg + j1 - 1), 0);
+            *dst = F::pad(__ldg(gidx + j1 - 1), __ldg(seg + j1 - 1));
         }
         cp_async_commit();
     };
@@ -303,10 +351,10 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     const int seg_before = (j0 > lo) ? __ldg(seg + j0 - 1) : ~cur;
     const int seg_after = (j1 < hi) ? __ldg(seg + j1) : 0;      // fetched now, needed at the very end
     bool head_open = (j0 > lo) && (seg_before == cur);
-    float4 acc[NT];
-    float4 oldv[NT];   // current contents of the output column of the run, fetched when the run starts
+    vec acc[NT];
+    vec oldv[NT];      // current contents of the output column of the run, fetched when the run starts
 #pragma unroll
-    for (int t = 0; t < NT; t++) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int t = 0; t < NT; t++) acc[t] = F::zero();
 
     // The read half of the output's read-modify-write is issued at the start of a
     // run and only consumed when the run is flushed, so its latency overlaps the
@@ -314,22 +362,22 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     // (runs shared with a neighbour go to `part` instead), so the value cannot
     // change in between.
     auto prefetch_out = [&]() {
-        const float4 *o = reinterpret_cast<const float4 *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
+        const vec *o = reinterpret_cast<const vec *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
 #pragma unroll
         for (int t = 0; t < NT; t++) oldv[t] = o[t * LPV];
     };
 
     auto flush = [&](bool tail_open) {
         if (!head_open && !tail_open) {
-            float4 *o = reinterpret_cast<float4 *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
+            vec *o = reinterpret_cast<vec *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
 #pragma unroll
             for (int t = 0; t < NT; t++) {
-                float4 old = oldv[t];
-                old.x += acc[t].x; old.y += acc[t].y; old.z += acc[t].z; old.w += acc[t].w;
+                vec old = oldv[t];
+                F::add(old, acc[t]);
                 o[t * LPV] = old;
             }
         } else {
-            float4 *p = reinterpret_cast<float4 *>(part + ((size_t)c * 2 + (head_open ? 0 : 1)) * K) + lane;
+            vec *p = reinterpret_cast<vec *>(part + ((size_t)c * 2 + (head_open ? 0 : 1)) * K) + lane;
 #pragma unroll
             for (int t = 0; t < NT; t++) p[t * LPV] = acc[t];
         }
@@ -347,12 +395,12 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
         worker_sync<LPV>(mask);
         const int4 *mt = meta[w][b & 1];
 
-        float4 x[2][U][NT];
+        vec x[2][U][NT];
         int4 e[2][U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
             e[0][u] = mt[u];
-            const float4 *d = reinterpret_cast<const float4 *>(Dl + (size_t)e[0][u].x * K);
+            const vec *d = reinterpret_cast<const vec *>(Dl + (size_t)e[0][u].x * K);
 #pragma unroll
             for (int t = 0; t < NT; t++) x[0][u][t] = __ldg(d + t * LPV);
         }
@@ -362,7 +410,7 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
 #pragma unroll
                 for (int u = 0; u < U; u++) {
                     e[(g + 1) & 1][u] = mt[(g + 1) * U + u];
-                    const float4 *d = reinterpret_cast<const float4 *>(Dl + (size_t)e[(g + 1) & 1][u].x * K);
+                    const vec *d = reinterpret_cast<const vec *>(Dl + (size_t)e[(g + 1) & 1][u].x * K);
 #pragma unroll
                     for (int t = 0; t < NT; t++) x[(g + 1) & 1][u][t] = __ldg(d + t * LPV);
                 }
@@ -370,21 +418,17 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const int4 m = e[g & 1][u];
-                if (m.z != cur) {
+                if (F::seg(m) != cur) {
                     flush(false);
-                    cur = m.z;
+                    cur = F::seg(m);
                     head_open = false;
                     prefetch_out();
 #pragma unroll
-                    for (int t = 0; t < NT; t++) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int t = 0; t < NT; t++) acc[t] = F::zero();
                 }
-                const float v = __int_as_float(m.y);
+                const S v = F::val(m);
 #pragma unroll
-                for (int t = 0; t < NT; t++) {
-                    const float4 xv = x[g & 1][u][t];
-                    acc[t].x = fmaf(v, xv.x, acc[t].x); acc[t].y = fmaf(v, xv.y, acc[t].y);
-                    acc[t].z = fmaf(v, xv.z, acc[t].z); acc[t].w = fmaf(v, xv.w, acc[t].w);
-                }
+                for (int t = 0; t < NT; t++) F::axpy(v, x[g & 1][u][t], acc[t]);
             }
         }
         worker_sync<LPV>(mask);   // everyone is done with this buffer before it is staged again
@@ -393,21 +437,23 @@ ga_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     flush(tail_open);
 }
 
-// Sampled dense-dense product, fast path (k = 4*32*NT, full warps).  The dot
+// Sampled dense-dense product, fast path (k = 32*NT 16-byte vectors, full warps).  The dot
 // products of 8 consecutive nonzeros are reduced together: three exchange
 // steps halve the number of live partials while doubling the lanes summed,
 // then two plain xor steps finish, 9 shuffles per 8 nonzeros instead of 40.
 // After four such groups lane l holds the result of nonzero (l&3)*8 + (l>>2)
 // of the batch, and the 32 results go out as one 128-byte store.
-template <int NT, int TPB, bool ACCUM>
+template <typename S, int NT, int U, int TPB, bool ACCUM>
 __global__ void __launch_bounds__(TPB)
 dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
-                      const float *__restrict__ A, const float *__restrict__ B,
-                      const int *__restrict__ ir, const int *__restrict__ ic, float *__restrict__ P) {
+                      const S *__restrict__ A, const S *__restrict__ B,
+                      const int *__restrict__ ir, const int *__restrict__ ic, S *__restrict__ P) {
+    typedef FastOps<S> F;
+    typedef typename F::vec vec;
     constexpr int LPV = 32;
-    constexpr int K = 4 * LPV * NT;
+    constexpr int K = F::VEC * LPV * NT;
     constexpr int WPB = TPB / LPV;
-    constexpr int U = 4;
+    static_assert(8 % U == 0, "U must divide 8");
     __shared__ int2 meta[WPB][2][LPV];     // {row, column}
 
     const int lane = threadIdx.x & 31;
@@ -418,8 +464,8 @@ dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     const long long j0 = c * (long long)chunk;
     const long long j1 = (j0 + chunk < nnz) ? j0 + chunk : nnz;
     const int nb = (int)((j1 - j0 + LPV - 1) / LPV);
-    const float *Al = A + lane * 4;
-    const float *Bl = B + lane * 4;
+    const S *Al = A + lane * F::VEC;
+    const S *Bl = B + lane * F::VEC;
 
     auto stage = [&](int buf, long long base) {
         const long long jj = base + lane;
@@ -434,9 +480,9 @@ dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
     };
 
     int cur = -1;
-    float4 bv[NT];
+    vec bv[NT];
 #pragma unroll
-    for (int t = 0; t < NT; t++) bv[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int t = 0; t < NT; t++) bv[t] = F::zero();
 
     stage(0, j0);
     for (int b = 0; b < nb; b++) {
@@ -452,27 +498,27 @@ dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
         // my own result slot of this batch; start its read-modify-write early
         const int myslot = (lane & 3) * 8 + (lane >> 2);
         const long long myj = base + myslot;
-        float old = 0.f;
+        S old = 0;
         if (ACCUM && myj < j1) old = P[myj];
-        float mine = 0.f;
+        S mine = 0;
 
-        float4 x[2][U][NT];
+        vec x[2][U][NT];
         int2 e[2][U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
             e[0][u] = mt[u];
-            const float4 *a = reinterpret_cast<const float4 *>(Al + (size_t)e[0][u].x * K);
+            const vec *a = reinterpret_cast<const vec *>(Al + (size_t)e[0][u].x * K);
 #pragma unroll
             for (int t = 0; t < NT; t++) x[0][u][t] = __ldg(a + t * LPV);
         }
-        float p[8];
+        S p[8];
 #pragma unroll
         for (int g = 0; g < LPV / U; g++) {
             if (g + 1 < LPV / U) {
 #pragma unroll
                 for (int u = 0; u < U; u++) {
                     e[(g + 1) & 1][u] = mt[(g + 1) * U + u];
-                    const float4 *a = reinterpret_cast<const float4 *>(Al + (size_t)e[(g + 1) & 1][u].x * K);
+                    const vec *a = reinterpret_cast<const vec *>(Al + (size_t)e[(g + 1) & 1][u].x * K);
 #pragma unroll
                     for (int t = 0; t < NT; t++) x[(g + 1) & 1][u][t] = __ldg(a + t * LPV);
                 }
@@ -482,42 +528,38 @@ dds_chunk_fast_kernel(long long nnz, int chunk, long long nchunks,
                 const int col = e[g & 1][u].y;
                 if (col != cur) {
                     cur = col;
-                    const float4 *bp = reinterpret_cast<const float4 *>(Bl + (size_t)cur * K);
+                    const vec *bp = reinterpret_cast<const vec *>(Bl + (size_t)cur * K);
 #pragma unroll
                     for (int t = 0; t < NT; t++) bv[t] = __ldg(bp + t * LPV);
                 }
-                float s = 0.f;
+                S s = 0;
 #pragma unroll
-                for (int t = 0; t < NT; t++) {
-                    const float4 xv = x[g & 1][u][t];
-                    s = fmaf(xv.x, bv[t].x, s); s = fmaf(xv.y, bv[t].y, s);
-                    s = fmaf(xv.z, bv[t].z, s); s = fmaf(xv.w, bv[t].w, s);
-                }
-                p[(g & 1) * U + u] = s;
+                for (int t = 0; t < NT; t++) s = F::dot(x[g & 1][u][t], bv[t], s);
+                p[(g * U + u) & 7] = s;        // position in the batch modulo 8 (compile-time: loops are unrolled)
             }
-            if (g & 1) {
-                // reduce the 8 partial dot products p[0..7] of nonzeros 8*(g/2) .. 8*(g/2)+7
+            if (((g * U + U - 1) & 7) == 7) {
+                // reduce the 8 partial dot products p[0..7] of the last 8 nonzeros
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const float give = (lane & 16) ? p[i] : p[i + 4];
-                    const float keep = (lane & 16) ? p[i + 4] : p[i];
+                    const S give = (lane & 16) ? p[i] : p[i + 4];
+                    const S keep = (lane & 16) ? p[i + 4] : p[i];
                     p[i] = keep + __shfl_xor_sync(mask, give, 16);
                 }
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
-                    const float give = (lane & 8) ? p[i] : p[i + 2];
-                    const float keep = (lane & 8) ? p[i + 2] : p[i];
+                    const S give = (lane & 8) ? p[i] : p[i + 2];
+                    const S keep = (lane & 8) ? p[i + 2] : p[i];
                     p[i] = keep + __shfl_xor_sync(mask, give, 8);
                 }
                 {
-                    const float give = (lane & 4) ? p[0] : p[1];
-                    const float keep = (lane & 4) ? p[1] : p[0];
+                    const S give = (lane & 4) ? p[0] : p[1];
+                    const S keep = (lane & 4) ? p[1] : p[0];
                     p[0] = keep + __shfl_xor_sync(mask, give, 4);
                 }
                 p[0] += __shfl_xor_sync(mask, p[0], 2);
                 p[0] += __shfl_xor_sync(mask, p[0], 1);
                 // lane l now holds the dot product of nonzero (l >> 2) of this group of 8
-                if ((lane & 3) == (g >> 1)) mine = p[0];
+                if ((lane & 3) == ((g * U + U - 1) >> 3)) mine = p[0];
             }
         }
         if (myj < j1) P[myj] = ACCUM ? old + mine : mine;

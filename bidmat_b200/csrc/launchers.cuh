@@ -14,13 +14,13 @@ namespace bidmat {
 // O[:, seg[j]] += val[j] * D[:, gidx[j]] with `part` holding 2*nchunks*k floats.
 constexpr int kFastThreads = 128;
 
-// k = 4*lpv*nt exactly and 16-byte aligned operands: the predicate-free kernels apply.
-inline bool fast_shape(int k, const Shape &s) { return s.vec == 4 && s.tiles == 1 && k == 4 * s.lpv * s.nt; }
+// k = vec*lpv*nt exactly with 16-byte vectors (4 floats / 2 doubles) and aligned operands:
+// the predicate-free kernels apply.
+inline bool fast_shape(int k, const Shape &s) { return s.vec > 1 && s.tiles == 1 && k == s.vec * s.lpv * s.nt; }
 
 // `count` nonzeros are processed: the whole list (range == nullptr, count == nnz) or
 // the slice [range[0], range[1]) read on the device.  The output column of a
-// nonzero is seg & segmask.  S is float or double; the predicate-free fast
-// kernels exist for float only.
+// nonzero is seg & segmask.  S is float or double.
 template <typename S>
 cudaError_t launch_ga(int k, long long nnz, const S *D, const S *val, const int *gidx,
                       const int *seg, S *O, S *part, int chunk, const Shape &s,
@@ -34,22 +34,20 @@ cudaError_t launch_ga(int k, long long nnz, const S *D, const S *val, const int 
     const long long nchunks = (count + chunk - 1) / chunk;
     dim3 grid(blocks_for(nchunks, s.lpv), s.tiles, 1);
     bool done = false;
-    if constexpr (std::is_same<S, float>::value) {
-        if (fast_shape(k, s) && ld_d == k && ld_o == k && !env_int("BIDMAT_B200_GENERIC", 0)) {
-            const int wpb = kFastThreads / s.lpv;
-            dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
-            ScopedSpan sp(label, st);
+    if (fast_shape(k, s) && ld_d == k && ld_o == k && !env_int("BIDMAT_B200_GENERIC", 0)) {
+        const int wpb = kFastThreads / s.lpv;
+        dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
+        ScopedSpan sp(label, st);
 #define CALL_FAST(LPV, NT, U, MINB)                                                                    \
-    ga_chunk_fast_kernel<LPV, NT, U, kFastThreads, MINB><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, D, val, \
-                                                                                        gidx, seg, O, part, range, segmask)
-            if (s.lpv == 8) { CALL_FAST(8, 1, 4, 0); }
-            else if (s.lpv == 16) { CALL_FAST(16, 1, 4, 0); }
-            else if (s.nt == 1) { CALL_FAST(32, 1, 4, 0); }
-            else if (s.nt == 2) { CALL_FAST(32, 2, 2, 5); }
-            else { CALL_FAST(32, 4, 1, 0); }
+    ga_chunk_fast_kernel<S, LPV, NT, U, kFastThreads, MINB><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, D, val, \
+                                                                                           gidx, seg, O, part, range, segmask)
+        if (s.lpv == 8) { CALL_FAST(8, 1, 4, 0); }
+        else if (s.lpv == 16) { CALL_FAST(16, 1, 4, 0); }
+        else if (s.nt == 1) { CALL_FAST(32, 1, 4, 0); }
+        else if (s.nt == 2) { CALL_FAST(32, 2, 2, 5); }
+        else { CALL_FAST(32, 4, 1, 0); }
 #undef CALL_FAST
-            done = true;
-        }
+        done = true;
     }
     if (!done) {
 #define CALL_GA(VEC, LPV, NT)                                                                   \
@@ -83,16 +81,18 @@ cudaError_t launch_dds(int k, long long nnz, const S *A, const S *B, const int *
     dim3 grid(blocks_for(nchunks, s.lpv), 1, 1);
     ScopedSpan sp("dds_chunk", st);
     bool done = false;
-    if constexpr (std::is_same<S, float>::value) {
-        if (fast_shape(k, s) && s.lpv == 32 && s.nt <= 2 && !env_int("BIDMAT_B200_GENERIC", 0)) {
-            const int wpb = kFastThreads / 32;
-            dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
-            if (s.nt == 1)
-                dds_chunk_fast_kernel<1, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
-            else
-                dds_chunk_fast_kernel<2, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
-            done = true;
-        }
+    // fp32: k = 128, 256; fp64: k = 64, 128, 256 (four vectors per lane, two nonzeros in flight)
+    const int max_nt = std::is_same<S, float>::value ? 2 : 4;
+    if (fast_shape(k, s) && s.lpv == 32 && s.nt <= max_nt && !env_int("BIDMAT_B200_GENERIC", 0)) {
+        const int wpb = kFastThreads / 32;
+        dim3 fgrid((unsigned)((nchunks + wpb - 1) / wpb), 1, 1);
+        if (s.nt == 1)
+            dds_chunk_fast_kernel<S, 1, 4, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
+        else if (s.nt == 2)
+            dds_chunk_fast_kernel<S, 2, 4, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
+        else if constexpr (!std::is_same<S, float>::value)
+            dds_chunk_fast_kernel<S, 4, 2, kFastThreads, ACCUM><<<fgrid, kFastThreads, 0, st>>>(nnz, chunk, nchunks, A, B, ir, ic, P);
+        done = true;
     }
     if (!done) {
 #define CALL_DDS(VEC, LPV, NT)                                                                  \

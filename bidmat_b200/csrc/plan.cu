@@ -297,11 +297,10 @@ int plan_run(bidmat_b200_plan *p, int k, int ncols, int nnz, const S *A, const S
     const int *seg = reinterpret_cast<const int *>(p->keys);
 
     // The predicate-free float kernel reads the values through the stored positions itself
-    // (BIDMAT_B200_PLAN_FUSED=0 switches that off); every other shape first brings them into
-    // the plan's order with one gather pass into scratch.
-    bool fast = false;
-    if constexpr (std::is_same<S, float>::value) fast = fast_shape(k, s) && !env_int("BIDMAT_B200_GENERIC", 0);
-    const bool fused = fast && env_int("BIDMAT_B200_PLAN_FUSED", 1) != 0;
+    // (BIDMAT_B200_PLAN_FUSED=0 switches that off); the double one and every other shape first
+    // bring them into the plan's order with one gather pass into scratch.
+    const bool fast = fast_shape(k, s) && !env_int("BIDMAT_B200_GENERIC", 0);
+    const bool fused = fast && std::is_same<S, float>::value && env_int("BIDMAT_B200_PLAN_FUSED", 1) != 0;
     if (part_index >= 0 && !fused) return (int)cudaErrorNotSupported;   // parts need the kernel that reads the values in place
     WorkspaceLease ws(fused ? 256 : pad256(n * sizeof(S)) + 256, st);
     if (ws.err != cudaSuccess) return (int)ws.err;
@@ -328,35 +327,37 @@ int plan_run(bidmat_b200_plan *p, int k, int ncols, int nnz, const S *A, const S
         if (nch == 0) continue;
         ScopedSpan sp("dsmultT_ga_chunk", st);
         bool done = false;
-        if constexpr (std::is_same<S, float>::value) {
-            if (fast) {
-                const int wpb = kFastThreads / s.lpv;
-                const unsigned fgrid = (unsigned)((nch + wpb - 1) / wpb);
-#define CALL_PLAN(LPV, NT, U, MINB)                                                                             \
-    do {                                                                                                        \
-        if (fused)                                                                                              \
-            ga_plan_fast_kernel<LPV, NT, U, kFastThreads, MINB, true, true><<<fgrid, kFastThreads, 0, st>>>(    \
-                nch, desc, A, Bdata, p->perm, p->cols, seg, C, part, segmask, storebit);                        \
-        else if (prefetch)                                                                                      \
-            ga_plan_fast_kernel<LPV, NT, U, kFastThreads, MINB, true, false><<<fgrid, kFastThreads, 0, st>>>(   \
-                nch, desc, A, vals, nullptr, p->cols, seg, C, part, segmask, storebit);                         \
-        else                                                                                                    \
-            ga_plan_fast_kernel<LPV, NT, U, kFastThreads, MINB, false, false><<<fgrid, kFastThreads, 0, st>>>(  \
-                nch, desc, A, vals, nullptr, p->cols, seg, C, part, segmask, storebit);                         \
+        if (fast) {
+            const int wpb = kFastThreads / s.lpv;
+            const unsigned fgrid = (unsigned)((nch + wpb - 1) / wpb);
+#define CALL_PLAN(LPV, NT, U, MINB)                                                                                \
+    do {                                                                                                           \
+        if constexpr (std::is_same<S, float>::value) {                                                             \
+            if (fused) {                                                                                           \
+                ga_plan_fast_kernel<S, LPV, NT, U, kFastThreads, MINB, true, true><<<fgrid, kFastThreads, 0, st>>>( \
+                    nch, desc, A, Bdata, p->perm, p->cols, seg, C, part, segmask, storebit);                       \
+                break;                                                                                             \
+            }                                                                                                      \
+        }                                                                                                          \
+        if (prefetch)                                                                                              \
+            ga_plan_fast_kernel<S, LPV, NT, U, kFastThreads, MINB, true, false><<<fgrid, kFastThreads, 0, st>>>(   \
+                nch, desc, A, vals, nullptr, p->cols, seg, C, part, segmask, storebit);                            \
+        else                                                                                                       \
+            ga_plan_fast_kernel<S, LPV, NT, U, kFastThreads, MINB, false, false><<<fgrid, kFastThreads, 0, st>>>(  \
+                nch, desc, A, vals, nullptr, p->cols, seg, C, part, segmask, storebit);                            \
     } while (0)
-                if (s.lpv == 8) CALL_PLAN(8, 1, 4, 0);
-                else if (s.lpv == 16) CALL_PLAN(16, 1, 4, 0);
-                else if (s.nt == 1) CALL_PLAN(32, 1, 4, 0);
-                else if (s.nt == 2) {
-                    // five CTAs of 128 threads per SM (<= 96 registers, a few spilled words) against
-                    // four without spills: BIDMAT_B200_PLAN_MINB picks, default 5 as for A*S
-                    if (env_int("BIDMAT_B200_PLAN_MINB", 5) == 4) CALL_PLAN(32, 2, 2, 4);
-                    else CALL_PLAN(32, 2, 2, 5);
-                }
-                else CALL_PLAN(32, 4, 1, 0);
-#undef CALL_PLAN
-                done = true;
+            if (s.lpv == 8) CALL_PLAN(8, 1, 4, 0);
+            else if (s.lpv == 16) CALL_PLAN(16, 1, 4, 0);
+            else if (s.nt == 1) CALL_PLAN(32, 1, 4, 0);
+            else if (s.nt == 2) {
+                // five CTAs of 128 threads per SM (<= 96 registers, a few spilled words) against
+                // four without spills: BIDMAT_B200_PLAN_MINB picks, default 5 as for A*S
+                if (env_int("BIDMAT_B200_PLAN_MINB", 5) == 4) CALL_PLAN(32, 2, 2, 4);
+                else CALL_PLAN(32, 2, 2, 5);
             }
+            else CALL_PLAN(32, 4, 1, 0);
+#undef CALL_PLAN
+            done = true;
         }
         if (!done) {
             dim3 grid(blocks_for(nch, s.lpv), s.tiles, 1);

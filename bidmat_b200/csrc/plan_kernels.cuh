@@ -174,8 +174,8 @@ __device__ __forceinline__ void prefetch_l2(const void *p) {
 }
 
 // ---------------------------------------------------------------------------
-// Gather-accumulate over the chunks of a plan, dense heights k = 4*LPV*NT with
-// 16-byte aligned operands (the shapes of ga_chunk_fast_kernel, which this kernel
+// Gather-accumulate over the chunks of a plan, dense heights k = VEC*LPV*NT (fp32 or
+// fp64, FUSED for fp32 only) with 16-byte aligned operands (the shapes of ga_chunk_fast_kernel, which this kernel
 // follows: cp.async-staged (index, value, segment) triples, gathers U columns
 // ahead of the FMAs, read half of the output's read-modify-write issued when a
 // run starts).  Differences:
@@ -193,16 +193,19 @@ __device__ __forceinline__ void prefetch_l2(const void *p) {
 //     (each a DRAM sector) overlap the gathers of this kernel, which leaves DRAM mostly
 //     idle, instead of costing a pass of their own (plan_permute_kernel).
 // ---------------------------------------------------------------------------
-template <int LPV, int NT, int U, int TPB, int MINB, bool PREFETCH, bool FUSED>
+template <typename S, int LPV, int NT, int U, int TPB, int MINB, bool PREFETCH, bool FUSED>
 __global__ void __launch_bounds__(TPB, MINB)
 ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
-                    const float *__restrict__ D, const float *__restrict__ val, const int *__restrict__ perm,
+                    const S *__restrict__ D, const S *__restrict__ val, const int *__restrict__ perm,
                     const int *__restrict__ gidx, const int *__restrict__ seg,
-                    float *__restrict__ O, float *__restrict__ part, unsigned segmask, unsigned storebit) {
-    constexpr int K = 4 * LPV * NT;
+                    S *__restrict__ O, S *__restrict__ part, unsigned segmask, unsigned storebit) {
+    typedef FastOps<S> F;
+    typedef typename F::vec vec;
+    static_assert(!FUSED || sizeof(S) == 4, "the staged record has room for a position only beside a 4-byte value");
+    constexpr int K = F::VEC * LPV * NT;
     constexpr int WPB = TPB / LPV;
     constexpr int G = LPV / U;
-    constexpr int LINES = (K * 4 + 127) / 128;     // 128-byte lines per output column
+    constexpr int LINES = (K * (int)sizeof(S) + 127) / 128;     // 128-byte lines per output column
     constexpr int NBUF = FUSED ? 3 : 2;            // staged batches of {index, value, segment, position}
     static_assert(LPV % U == 0, "U must divide LPV");
     __shared__ int4 meta[WPB][NBUF][LPV];
@@ -216,7 +219,7 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
     const int4 dc = __ldg(desc + c);
     const long long j0 = dc.x, j1 = dc.y;
     const int nb = (int)((j1 - j0 + LPV - 1) / LPV);
-    const float *Dl = D + lane * 4;
+    const S *Dl = D + lane * F::VEC;
 
     // Every call commits exactly one cp.async group, also for a batch beyond the chunk
     // (an empty group), so the wait counts below do not depend on where the chunk ends.
@@ -226,12 +229,12 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
             int4 *dst = &meta[w][batch % NBUF][lane];
             if (jj < j1) {
                 cp_async4(&dst->x, gidx + jj);
-                cp_async4(&dst->z, seg + jj);
+                F::stage_seg(dst, seg + jj);
                 if (FUSED) cp_async4(&dst->w, perm + jj);
-                else cp_async4(&dst->y, val + jj);
+                else F::stage_val(dst, val + jj);
             } else {
                 // padding of the last batch: repeat the last nonzero with value 0
-                *dst = make_int4(__ldg(gidx + j1 - 1), 0, __ldg(seg + j1 - 1), -1);
+                *dst = F::pad(__ldg(gidx + j1 - 1), __ldg(seg + j1 - 1));
             }
         }
         cp_async_commit();
@@ -240,21 +243,21 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
         if (batch < nb) {
             const long long jj = j0 + (long long)batch * LPV + lane;
             int4 *dst = &meta[w][batch % NBUF][lane];
-            if (jj < j1) cp_async4(&dst->y, val + dst->w);     // this lane's own position: visible after its wait
+            if (jj < j1) F::stage_val(dst, val + dst->w);      // this lane's own position: visible after its wait
         }
         cp_async_commit();
     };
 
     int cur = __ldg(seg + j0);
     bool head_open = dc.z >= 0;
-    float4 acc[NT];
-    float4 oldv[NT];
+    vec acc[NT];
+    vec oldv[NT];
 #pragma unroll
-    for (int t = 0; t < NT; t++) { acc[t] = make_float4(0.f, 0.f, 0.f, 0.f); oldv[t] = acc[t]; }
+    for (int t = 0; t < NT; t++) { acc[t] = F::zero(); oldv[t] = acc[t]; }
 
     auto prefetch_out = [&]() {
         if (((unsigned)cur & storebit) == 0u) {
-            const float4 *o = reinterpret_cast<const float4 *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
+            const vec *o = reinterpret_cast<const vec *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
 #pragma unroll
             for (int t = 0; t < NT; t++) oldv[t] = o[t * LPV];
         }
@@ -262,20 +265,20 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
 
     auto flush = [&](bool tail_open) {
         if (!head_open && !tail_open) {
-            float4 *o = reinterpret_cast<float4 *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
+            vec *o = reinterpret_cast<vec *>(O + (size_t)((unsigned)cur & segmask) * K) + lane;
             if (((unsigned)cur & storebit) != 0u) {
 #pragma unroll
                 for (int t = 0; t < NT; t++) o[t * LPV] = acc[t];
             } else {
 #pragma unroll
                 for (int t = 0; t < NT; t++) {
-                    float4 old = oldv[t];
-                    old.x += acc[t].x; old.y += acc[t].y; old.z += acc[t].z; old.w += acc[t].w;
+                    vec old = oldv[t];
+                    F::add(old, acc[t]);
                     o[t * LPV] = old;
                 }
             }
         } else {
-            float4 *p = reinterpret_cast<float4 *>(part + (size_t)(head_open ? dc.z : dc.w) * K) + lane;
+            vec *p = reinterpret_cast<vec *>(part + (size_t)(head_open ? dc.z : dc.w) * K) + lane;
 #pragma unroll
             for (int t = 0; t < NT; t++) p[t * LPV] = acc[t];
         }
@@ -322,12 +325,12 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
         worker_sync<LPV>(mask);
         const int4 *mt = meta[w][b % NBUF];
 
-        float4 x[2][U][NT];
+        vec x[2][U][NT];
         int4 e[2][U];
 #pragma unroll
         for (int u = 0; u < U; u++) {
             e[0][u] = mt[u];
-            const float4 *d = reinterpret_cast<const float4 *>(Dl + (size_t)e[0][u].x * K);
+            const vec *d = reinterpret_cast<const vec *>(Dl + (size_t)e[0][u].x * K);
 #pragma unroll
             for (int t = 0; t < NT; t++) x[0][u][t] = __ldg(d + t * LPV);
         }
@@ -337,7 +340,7 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
 #pragma unroll
                 for (int u = 0; u < U; u++) {
                     e[(g + 1) & 1][u] = mt[(g + 1) * U + u];
-                    const float4 *d = reinterpret_cast<const float4 *>(Dl + (size_t)e[(g + 1) & 1][u].x * K);
+                    const vec *d = reinterpret_cast<const vec *>(Dl + (size_t)e[(g + 1) & 1][u].x * K);
 #pragma unroll
                     for (int t = 0; t < NT; t++) x[(g + 1) & 1][u][t] = __ldg(d + t * LPV);
                 }
@@ -345,7 +348,7 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
             if (PREFETCH && g == G / 2) {
                 // output columns of the runs that start in the next batch, into L2
                 int pseg = __shfl_up_sync(mask, nseg, 1, LPV);
-                if (lane == 0) pseg = mt[LPV - 1].z;
+                if (lane == 0) pseg = F::seg(mt[LPV - 1]);
                 if (nvalid && nseg != pseg && ((unsigned)nseg & storebit) == 0u) {
                     const char *o = reinterpret_cast<const char *>(O + (size_t)((unsigned)nseg & segmask) * K);
 #pragma unroll
@@ -355,21 +358,17 @@ ga_plan_fast_kernel(int nchunks, const int4 *__restrict__ desc,
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const int4 m = e[g & 1][u];
-                if (m.z != cur) {
+                if (F::seg(m) != cur) {
                     flush(false);
-                    cur = m.z;
+                    cur = F::seg(m);
                     head_open = false;
                     prefetch_out();
 #pragma unroll
-                    for (int t = 0; t < NT; t++) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int t = 0; t < NT; t++) acc[t] = F::zero();
                 }
-                const float v = __int_as_float(m.y);
+                const S v = F::val(m);
 #pragma unroll
-                for (int t = 0; t < NT; t++) {
-                    const float4 xv = x[g & 1][u][t];
-                    acc[t].x = fmaf(v, xv.x, acc[t].x); acc[t].y = fmaf(v, xv.y, acc[t].y);
-                    acc[t].z = fmaf(v, xv.z, acc[t].z); acc[t].w = fmaf(v, xv.w, acc[t].w);
-                }
+                for (int t = 0; t < NT; t++) F::axpy(v, x[g & 1][u][t], acc[t]);
             }
         }
         worker_sync<LPV>(mask);

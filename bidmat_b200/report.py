@@ -162,6 +162,9 @@ def extras(args, dev, stream, peak, peak_src):
         if e != 0:
             raise RuntimeError(_lib.error_string(e))
 
+    import ctypes
+    plan64 = ctypes.c_void_p(0)
+    ck(L.bidmat_b200_dsmultT_plan_create(k, n, nnz, m, ptr(S.pir), ptr(S.pic), 8, None, ctypes.byref(plan64)))
     cases = [
         ("transpose (GSMat.t)", lambda: S.t, nnz * 24.0, None),
         ("spsum columns", lambda: ck(L.bidmat_b200_spsum(m, n, nnz, ptr(S.pir), ptr(S.pic), ptr(S.pdata), ptr(sums_c), 1)),
@@ -185,6 +188,10 @@ def extras(args, dev, stream, peak, peak_src):
          nnz * (8.0 * k + 24) + n * 8.0 * k, 2.0 * k * nnz),
         ("B*^S fp64", lambda: ck(L.bidmat_b200_dsmultT_f64(k, n, nnz, ptr(B64), ptr(d64), ptr(S.pir), ptr(S.pic), ptr(G64))),
          nnz * (8.0 * k + 16) + m * 16.0 * k, 2.0 * k * nnz),
+        ("B*^S fp64 (prepared plan)",
+         lambda: (ck(L.bidmat_b200_dsmultT_planned_f64(plan64, k, n, nnz, ptr(B64), ptr(d64), ptr(G64), 0, None)),
+                  torch.cuda.synchronize(dev)),
+         nnz * (8.0 * k + 16) + m * 16.0 * k, 2.0 * k * nnz),
     ]
     for name, fn, nbytes, flops in cases:
         ms = _time(fn, torch.cuda.current_stream(dev), args.reps, args.warmup)
@@ -197,6 +204,7 @@ def extras(args, dev, stream, peak, peak_src):
         if flops:
             out["gflops"] = flops / (ms * 1e-3) / 1e9
         print(json.dumps(out), flush=True)
+    ck(L.bidmat_b200_plan_destroy(plan64))
     return 0
 
 

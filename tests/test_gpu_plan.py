@@ -173,6 +173,43 @@ def test_planned_product_double_precision(cuda_device):
     plan.close()
 
 
+@pytest.mark.parametrize("k", [16, 64, 128, 256])
+@pytest.mark.parametrize("chunk,colblock", [(0, 0), (32, 16)])
+def test_planned_product_double_precision_at_the_predicate_free_heights(cuda_device, k, chunk, colblock, monkeypatch):
+    """k = 2*lanes*vectors in fp64 takes the predicate-free plan kernel (values permuted by a pass of
+    their own); tiny chunks and column blocks force split runs, slots and both fix-up levels."""
+    if chunk:
+        monkeypatch.setenv("BIDMAT_B200_CHUNK", str(chunk))
+    if colblock:
+        monkeypatch.setenv("BIDMAT_B200_COLBLOCK_COLS", str(colblock))
+    rng = np.random.default_rng(100 + k + chunk)
+    m, n = 90, 130
+    jc, ir, data = random_csc(m, n, 0.35, rng, empty_cols=(3, 77))
+    S = DeviceCSC(m, n, jc, ir, data, cuda_device)
+    B = rng.standard_normal((n, k))
+    G0 = rng.standard_normal((m, k))
+    d64 = data.astype(np.float64) + rng.uniform(0, 1e-9, len(data))
+    dd = dev(d64, cuda_device)
+    plan = Plan(k, S, elem=8)
+    absS = np.zeros((m, n))
+    np.add.at(absS, (ir, S.ic_h), np.abs(d64))
+    scale = absS @ np.abs(B)
+    G = plan.run(dev(B, cuda_device), S, dev(G0, cuda_device), 0, dd).cpu().numpy()
+    want = oracle.dsmultT_d(B, d64, ir, jc, m, out=G0.copy())
+    assert_close_scaled(G, want, scale + np.abs(G0), 1e-12, "planned f64 B*^S k=%d" % k)
+    # overwrite mode on a dirty buffer: rows the matrix touches equal the product, the others keep their contents
+    Gd = plan.run(dev(B, cuda_device), S, dev(G0, cuda_device), OVERWRITE, dd).cpu().numpy()
+    want0 = oracle.dsmultT_d(B, d64, ir, jc, m)
+    touched = np.zeros(m, dtype=bool)
+    touched[ir] = True
+    assert_close_scaled(Gd[touched], want0[touched], scale[touched], 1e-12, "planned f64 overwrite k=%d" % k)
+    assert np.array_equal(Gd[~touched], G0[~touched])
+    # same bits on a second run
+    G2 = plan.run(dev(B, cuda_device), S, dev(G0, cuda_device), 0, dd).cpu().numpy()
+    assert np.array_equal(G.view(np.int64), G2.view(np.int64))
+    plan.close()
+
+
 def test_plan_verification_and_misuse(cuda_device):
     rng = np.random.default_rng(4)
     k, m, n = 64, 40, 30
