@@ -45,7 +45,7 @@ def test_sdoprow_sdopcol_and_scalar(cuda_device, opn):
     assert L.bidmat_b200_sdoprow(m, n, 0, 0, 0, 0, 1, 0) == 0
 
 
-@pytest.mark.parametrize("m,n,dens", [(50, 40, 0.3), (3000, 2000, 0.01), (7, 50000, 0.3)])
+@pytest.mark.parametrize("m,n,dens", [(50, 40, 0.3), (3000, 2000, 0.01), (7, 50000, 0.3), (600, 700, 0.06), (20000, 37, 0.4)])
 def test_spsum_rows_and_columns(cuda_device, m, n, dens, monkeypatch):
     from bidmat_b200 import _lib
     L = _lib.lib
@@ -73,6 +73,29 @@ def test_spsum_rows_and_columns(cuda_device, m, n, dens, monkeypatch):
         P64 = dev(P.astype(np.float64), cuda_device)
         assert L.bidmat_b200_spsum_f64(m, n, S.nnz, S.ir.data_ptr(), S.ic.data_ptr(), P64.data_ptr(), B64.data_ptr(), nn) == 0
         assert np.all(np.abs(B64.cpu().numpy() - want) <= 1e-13 * scale + 1e-30)
+
+
+@pytest.mark.parametrize("skip", [1, 2, 3])
+def test_spsum_with_index_and_value_lists_that_start_off_a_16_byte_boundary(cuda_device, skip):
+    """The column sums read whole 16-byte vectors only where the lists allow it: lists that start 4, 8 or
+    12 bytes into a vector (a view that drops the first nonzeros) take the element-wise loads."""
+    from bidmat_b200 import _lib
+    L = _lib.lib
+    rng = np.random.default_rng(70 + skip)
+    m, n = 400, 900
+    jc, ir, data = random_csc(m, n, 0.05, rng, empty_cols=(0, 5))
+    S = DeviceCSC(m, n, jc, ir, data, cuda_device)
+    P = rng.standard_normal(S.nnz).astype(np.float32)
+    dP = dev(P, cuda_device)
+    start = rng.standard_normal(n).astype(np.float32)
+    B = dev(start.copy(), cuda_device)
+    assert L.bidmat_b200_spsum(m, n, S.nnz - skip, S.ir.data_ptr() + 4 * skip, S.ic.data_ptr() + 4 * skip,
+                               dP.data_ptr() + 4 * skip, B.data_ptr(), 1) == 0
+    want = start.astype(np.float64).copy()
+    np.add.at(want, S.ic_h[skip:], P[skip:].astype(np.float64))
+    scale = np.abs(start).astype(np.float64)
+    np.add.at(scale, S.ic_h[skip:], np.abs(P[skip:]).astype(np.float64))
+    assert np.all(np.abs(B.cpu().numpy() - want) <= 1e-5 * scale + 1e-30)
 
 
 @pytest.mark.parametrize("opn", [0, 2, 3, 10, 13])
