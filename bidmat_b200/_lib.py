@@ -49,6 +49,8 @@ _SIGNATURES = {
     "bidmat_b200_peer_allreduce_sum_rows": (_c_int, [_c_int, _c_int, ctypes.POINTER(ctypes.c_ulonglong), _c_int,
                                                      ctypes.c_longlong, _vp, _c_int, _vp]),
     "bidmat_b200_mc_allreduce_sum": (_c_int, [_c_int, _c_int, _vp, ctypes.c_longlong, _c_int, _vp]),
+    "bidmat_b200_mc_allreduce_sum_range": (_c_int, [_c_int, _c_int, _vp, ctypes.c_longlong, ctypes.c_longlong, _c_int,
+                                                    _vp]),
     "bidmat_b200_plan_clear_untouched": (_c_int, [_vp, _c_int, _vp, _vp]),
     "bidmat_b200_peer_allreduce_sum_rows_range": (_c_int, [_c_int, _c_int, ctypes.POINTER(ctypes.c_ulonglong), _c_int,
                                                            ctypes.c_longlong, _vp, ctypes.c_longlong, ctypes.c_longlong,

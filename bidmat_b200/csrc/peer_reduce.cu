@@ -96,9 +96,9 @@ peer_sum_rows_kernel(PeerPtrs peers, long long v_begin, long long v_end, int vec
 // traffic).  Per GPU and direction about half as many bytes cross NVLink as with peer loads
 // and stores.  One GPU reduces each element and all receive its result, so the ranks end
 // bit-identical; the order of the additions inside the switch is the hardware's.
+template <int UNROLL>
 __global__ void __launch_bounds__(256)
 mc_sum_kernel(float *mc, long long v_begin, long long v_end) {
-    constexpr int UNROLL = 4;
     const long long stride = (long long)gridDim.x * blockDim.x;
     float4 *p = reinterpret_cast<float4 *>(mc);
     for (long long v0 = v_begin + (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < v_end; v0 += stride * UNROLL) {
@@ -140,22 +140,35 @@ int peer_args(int world, int rank, const unsigned long long *peer_addresses, lon
 
 }  // namespace
 
-extern "C" int bidmat_b200_mc_allreduce_sum(int world, int rank, void *multicast_address, long long count, int ctas,
-                                            bidmat_stream_t stream) {
-    if (world < 1 || rank < 0 || rank >= world || count < 0 || count % 4 != 0 || !multicast_address ||
-        (reinterpret_cast<uintptr_t>(multicast_address) & 15u))
+extern "C" int bidmat_b200_mc_allreduce_sum_range(int world, int rank, void *multicast_address, long long first,
+                                                  long long count, int ctas, bidmat_stream_t stream) {
+    if (world < 1 || rank < 0 || rank >= world || first < 0 || first % 4 != 0 || count < 0 || count % 4 != 0 ||
+        !multicast_address || (reinterpret_cast<uintptr_t>(multicast_address) & 15u))
         return (int)cudaErrorInvalidValue;
     if (count == 0 || world == 1) return 0;
+    // the 16-byte vectors of the range, cut into `world` slices: this rank reduces slice `rank`
     const long long nvec = count / 4;
     const long long per = (nvec + world - 1) / world;
-    const long long v_begin = per * rank < nvec ? per * rank : nvec;
-    const long long v_end = v_begin + per < nvec ? v_begin + per : nvec;
+    long long v_begin = per * rank < nvec ? per * rank : nvec;
+    long long v_end = v_begin + per < nvec ? v_begin + per : nvec;
     if (v_end <= v_begin) return 0;
+    v_begin += first / 4;
+    v_end += first / 4;
     if (ctas <= 0) ctas = (world >= 8) ? 96 : 64;     // measured on 8 GPUs: 32 CTAs leave 0.8 ms of the sum exposed, 96 none
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : cudaStreamPerThread;
-    mc_sum_kernel<<<ctas, 256, 0, st>>>(static_cast<float *>(multicast_address), v_begin, v_end);
+    // 16-byte reductions in flight per thread: BIDMAT_B200_MC_UNROLL = 4 (default), 8 or 16
+    const int unroll = env_int("BIDMAT_B200_MC_UNROLL", 4);
+    float *mc = static_cast<float *>(multicast_address);
+    if (unroll >= 16) mc_sum_kernel<16><<<ctas, 256, 0, st>>>(mc, v_begin, v_end);
+    else if (unroll >= 8) mc_sum_kernel<8><<<ctas, 256, 0, st>>>(mc, v_begin, v_end);
+    else mc_sum_kernel<4><<<ctas, 256, 0, st>>>(mc, v_begin, v_end);
     g_launches += 1;
     return (int)cudaGetLastError();
+}
+
+extern "C" int bidmat_b200_mc_allreduce_sum(int world, int rank, void *multicast_address, long long count, int ctas,
+                                            bidmat_stream_t stream) {
+    return bidmat_b200_mc_allreduce_sum_range(world, rank, multicast_address, 0, count, ctas, stream);
 }
 
 extern "C" int bidmat_b200_peer_allreduce_sum_rows_range(int world, int rank, const unsigned long long *peer_addresses,

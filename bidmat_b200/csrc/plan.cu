@@ -41,7 +41,8 @@ struct bidmat_b200_plan {
     // host copies for running a single-block plan in row ranges (bidmat_b200_plan_row_parts)
     std::vector<int> h_chunk_row;      // row of the first nonzero of a chunk, -1 when the chunk starts inside a row
     std::vector<int> h_group_row, h_group_run0;
-    std::vector<int> part_chunk, part_run, part_group, part_row;   // bounds per part, nparts + 1 entries each
+    std::vector<int> part_chunk, part_run, part_group, part_row, part_clear;   // bounds per part, nparts + 1 entries each
+    std::vector<int> h_clear_rows;  // host copy of clear_rows (ascending in a single-block plan)
     int nchunks = 0, nruns = 0, ngroups = 0, nslots = 0, nclear = 0;
     long long touched_rows = 0;
     long long row_runs = 0;        // runs of equal (column block, row): each one updates its output column once
@@ -238,6 +239,7 @@ int plan_create(int k, int ncols, int nnz, int m, const int *Bir, const int *Bic
     p->h_group_run0.resize(h_groups.size());
     for (size_t g = 0; g < h_groups.size(); g++) { p->h_group_row[g] = h_groups[g].x; p->h_group_run0[g] = h_groups[g].y; }
     p->nclear = (int)h_clear.size();
+    p->h_clear_rows = h_clear;
     for (int r = 0; r < m; r++) p->touched_rows += (h_first[r] != kNoBlock);
 
     PLAN_CK(plan_alloc(p, &p->desc, (size_t)total));
@@ -311,10 +313,19 @@ int plan_run(bidmat_b200_plan *p, int k, int ncols, int nnz, const S *A, const S
         else plan_permute_kernel<S><<<148 * 16, 256, 0, st>>>((long long)nnz, p->perm, Bdata, vals);
         g_launches += 1;
     }
-    if (storebit && p->nclear > 0 && part_index <= 0) {
-        plan_clear_rows_kernel<S><<<(unsigned)(((size_t)p->nclear * 32 + 255) / 256), 256, 0, st>>>(k, p->nclear,
-                                                                                                   p->clear_rows, C);
-        g_launches += 1;
+    {
+        // rows whose first run is split accumulate through the fix-up: an overwriting call clears them
+        // first (a row range clears its own, so the ranges may run in any order)
+        int clear0 = 0, nclear = p->nclear;
+        if (part_index >= 0) {
+            clear0 = p->part_clear[part_index];
+            nclear = p->part_clear[part_index + 1] - clear0;
+        }
+        if (storebit && nclear > 0) {
+            plan_clear_rows_kernel<S><<<(unsigned)(((size_t)nclear * 32 + 255) / 256), 256, 0, st>>>(k, nclear,
+                                                                                                     p->clear_rows + clear0, C);
+            g_launches += 1;
+        }
     }
     const bool prefetch = env_int("BIDMAT_B200_PLAN_PREFETCH", 1) != 0;
     for (int b = 0; b < p->lay.nblocks; b++) {
@@ -428,14 +439,16 @@ int bidmat_b200_plan_row_parts(bidmat_b200_plan_t p, int nparts, int *row_bounds
     const int actual = (int)chunk.size();
     chunk.push_back(p->nchunks);
     row.push_back(p->m);
-    std::vector<int> grp(1, 0), run(1, 0);
+    std::vector<int> grp(1, 0), run(1, 0), clr(1, 0);
     for (int i = 1; i <= actual; i++) {
+        clr.push_back((int)(std::lower_bound(p->h_clear_rows.begin(), p->h_clear_rows.end(), row[(size_t)i]) -
+                            p->h_clear_rows.begin()));
         const int g = (int)(std::lower_bound(p->h_group_row.begin(), p->h_group_row.end(), row[(size_t)i]) -
                             p->h_group_row.begin());
         grp.push_back(g);
         run.push_back(g < p->ngroups ? p->h_group_run0[(size_t)g] : p->nruns);
     }
-    p->part_chunk = chunk; p->part_row = row; p->part_group = grp; p->part_run = run;
+    p->part_chunk = chunk; p->part_row = row; p->part_group = grp; p->part_run = run; p->part_clear = clr;
     for (int i = 0; i <= actual; i++) row_bounds[i] = row[(size_t)i];
     for (int i = actual + 1; i <= nparts; i++) row_bounds[i] = p->m;
     return actual == nparts ? 0 : (int)cudaErrorNotSupported;

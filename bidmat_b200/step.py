@@ -94,28 +94,33 @@ class PathStep:
                 self.peer = None
         if self.peer is None:
             self.G = torch.zeros((shard.m, k), dtype=torch.float32, device=dev)
-        # A single-block plan (one rank's shard on many GPUs) runs in row ranges, and the sum of a
-        # range starts while the later ranges are still being multiplied.  The ranks agree on the
-        # ranges once: the smallest of their bounds, so a range is complete everywhere when summed.
+        # A single-block plan (one rank's shard on many GPUs) can run in row ranges of equal work, the
+        # sum of a range starting while the other ranges are still being multiplied.  The ranges run
+        # from the last to the first: row popularity falls with the row index in the workloads this
+        # path sees (words by frequency), so the last range holds nearly all the rows, i.e. nearly
+        # all the bytes to sum, and its sum gets the longest head start.  The ranks agree on the
+        # ranges once: the LARGEST of their bounds, so that a range summed after the local ranges
+        # from it upwards are done is complete on every rank.  BIDMAT_B200_PIPE_PARTS=n turns it on.
+        # Off by default.  Measured on 8 GPUs with the in-switch sum: B*^S and its sum alone take
+        # 3.19 ms in 2 ranges against 3.84 ms in one piece, but the whole step 4.17 - 4.37 ms against
+        # 4.03 ms: beside the sum's traffic the second range and A*S + DDS run that much slower, so
+        # what the earlier start gains is lost again (3 ranges: 4.87 ms; peer loads/stores of the
+        # touched rows in 4 ranges, first range first: 5.13 against 4.87 ms).
+        self.mc = self.peer is not None and bool(self.peer["mc"])
         self.parts = None
         self._pending = None
-        # (BIDMAT_B200_PIPE_PARTS=n turns it on; measured on 8 GPUs it does not pay: 5.13 ms per step
-        # with 4 ranges against 4.87 ms without, the extra rank synchronisations cost more than the
-        # earlier start gains, so it is off by default)
         nparts = int(os.environ.get("BIDMAT_B200_PIPE_PARTS", "0"))
-        if self.peer is not None and self.touched is not None and nparts > 1:
+        if self.peer is not None and (self.touched is not None or self.mc) and nparts > 1:
             import ctypes
             import torch.distributed as dist
             bounds = (ctypes.c_int * (nparts + 1))()
             rc = _L.bidmat_b200_plan_row_parts(self.plan.handle, nparts, bounds)
             t = torch.tensor([0 if rc == 0 else 1] + [int(b) for b in bounds], dtype=torch.int64, device=dev)
-            t[0] = -t[0]                      # MIN over ranks: -1 as soon as one rank cannot
-            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)      # t[0] = 1 as soon as one rank cannot
             if int(t[0]) == 0:
                 self.parts = [int(v) for v in t[1:]]
                 self.parts[0], self.parts[-1] = 0, shard.m
         # clear G every step?  Not when the plan overwrites and nobody reads the untouched rows.
-        self.mc = self.peer is not None and bool(self.peer["mc"])
         self.overwrite = self.plan is not None and (group is None or (self.peer is not None and
                                                                      (self.touched is not None or self.mc)))
 
@@ -212,13 +217,18 @@ class PathStep:
                                                  self.stream.cuda_stream), "dsmultT")
 
     def _dsmultT_in_parts(self, vals):
-        """B*^S range of rows after range of rows; the sum over the ranks of a range is queued
-        on the side stream as soon as the range is done here (and, by the rank synchronisation
-        in front of it, everywhere)."""
+        """B*^S range of rows after range of rows, last range first; the sum over the ranks of a
+        range is queued on the side stream as soon as the range is done here (and, by the rank
+        synchronisation in front of it, everywhere)."""
         import torch.distributed as dist
         S, pr = self.S, self.peer
         nparts = len(self.parts) - 1
-        for r in range(nparts):
+        if self.mc:
+            with torch.cuda.stream(self.stream):
+                # the switch adds whole ranges: rows this rank does not write must be zero
+                _ck(_L.bidmat_b200_plan_clear_untouched(self.plan.handle, self.k, self.G.data_ptr(),
+                                                        self.stream.cuda_stream), "plan_clear_untouched")
+        for r in reversed(range(nparts)):
             with torch.cuda.stream(self.stream):
                 _ck(_L.bidmat_b200_dsmultT_planned_part(self.plan.handle, self.k, S.n, S.nnz, self.B.data_ptr(),
                                                         vals.data_ptr(), self.G.data_ptr(), 1, r,
@@ -229,10 +239,16 @@ class PathStep:
                 pr["comm"].wait_event(done)
                 before = dist.all_reduce(pr["flag"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
                 before.wait()
-                _ck(_L.bidmat_b200_peer_allreduce_sum_rows_range(pr["world"], pr["rank"], pr["addrs"], self.k, S.m,
-                                                                 self.touched.data_ptr(), self.parts[r],
-                                                                 self.parts[r + 1], pr["ctas"], pr["comm"].cuda_stream),
-                    "peer_allreduce_sum_rows_range")
+                if self.mc:
+                    _ck(_L.bidmat_b200_mc_allreduce_sum_range(pr["world"], pr["rank"], pr["mc"], self.parts[r] * self.k,
+                                                              (self.parts[r + 1] - self.parts[r]) * self.k, pr["ctas"],
+                                                              pr["comm"].cuda_stream), "mc_allreduce_sum_range")
+                else:
+                    _ck(_L.bidmat_b200_peer_allreduce_sum_rows_range(pr["world"], pr["rank"], pr["addrs"], self.k, S.m,
+                                                                     self.touched.data_ptr(), self.parts[r],
+                                                                     self.parts[r + 1], pr["ctas"],
+                                                                     pr["comm"].cuda_stream),
+                        "peer_allreduce_sum_rows_range")
         with torch.cuda.stream(pr["comm"]):
             self._pending = dist.all_reduce(pr["flag"], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
 

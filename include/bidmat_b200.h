@@ -193,9 +193,9 @@ BIDMAT_B200_API int bidmat_b200_plan_touched_rows(bidmat_b200_plan_t plan, unsig
  * rank's shard on many GPUs) can be run in `nparts` consecutive ROW RANGES of the result:
  * plan_row_parts fixes the ranges (row_bounds[0..nparts], ascending, 0 and m at the ends) and
  * planned_part computes the columns of C in range `part` completely (its chunks, then the fix-up of
- * the split rows inside it).  Calling the parts 0 .. nparts-1 in order on one stream gives what
- * bidmat_b200_dsmultT_planned gives; a consumer of the first rows (the sum over the ranks) can
- * start while the later parts still run.  cudaErrorNotSupported (801): several column blocks, a
+ * the split rows inside it, with BIDMAT_B200_PLAN_OVERWRITE the clearing of its never-stored rows).
+ * Calling every part once, in any order, on one stream gives what bidmat_b200_dsmultT_planned gives;
+ * a consumer of finished rows (the sum over the ranks) can start while the other parts still run.  cudaErrorNotSupported (801): several column blocks, a
  * shape other than fp32 with nrows in {32 .. 512} and aligned pointers, or fewer chunks than parts. */
 BIDMAT_B200_API int bidmat_b200_plan_row_parts(bidmat_b200_plan_t plan, int nparts, int *row_bounds);
 BIDMAT_B200_API int bidmat_b200_dsmultT_planned_part(bidmat_b200_plan_t plan, int nrows, int ncols, int nnz,
@@ -284,6 +284,10 @@ BIDMAT_B200_API int bidmat_b200_peer_allreduce_sum_rows_range(int world, int ran
  * rules as bidmat_b200_peer_allreduce_sum. */
 BIDMAT_B200_API int bidmat_b200_mc_allreduce_sum(int world, int rank, void *multicast_address, long long count,
                                                  int ctas, bidmat_stream_t stream);
+/* The same over the floats [first, first + count) of the buffers only (both multiples of 4): the rows
+ * of a row range of a prepared product (bidmat_b200_dsmultT_planned_part) once every rank has computed them. */
+BIDMAT_B200_API int bidmat_b200_mc_allreduce_sum_range(int world, int rank, void *multicast_address, long long first,
+                                                       long long count, int ctas, bidmat_stream_t stream);
 
 /* Structure helpers on the device (the steps BIDMat performs around the path
  * with cuSPARSE csr2coo and a host loop: GSMat.fromSMat, GSMat.scala:639, and

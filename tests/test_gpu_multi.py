@@ -45,12 +45,13 @@ def _worker(rank, world, port, q):
             # NCCL; the library's sum through the switch (where the buffers have a multicast
             # mapping); the library's sum over peer loads and stores of the touched rows
             for mode, peer, mc, parts in (("nccl", False, "0", "0"), ("switch", True, "1", "0"), ("rows", True, "0", "0"),
-                                          ("rows_in_parts", True, "0", "4")):
+                                          ("rows_in_parts", True, "0", "4"), ("switch_in_parts", True, "1", "3")):
                 os.environ["BIDMAT_B200_PEER_MC"] = mc
                 os.environ["BIDMAT_B200_PIPE_PARTS"] = parts
                 st = pstep.PathStep(p.k, shard, p.A, B_local, stream, dist.group.WORLD, peer_reduce=peer)
-                kinds[mode] = "switch" if st.mc else (("rows in %d parts" % (len(st.parts) - 1) if st.parts else "rows")
-                                                      if st.touched is not None else "nccl" if st.peer is None else "dense")
+                in_parts = " in %d parts" % (len(st.parts) - 1) if st.parts else ""
+                kinds[mode] = ("switch" + in_parts) if st.mc else (("rows" + in_parts) if st.touched is not None
+                                                                   else "nccl" if st.peer is None else "dense")
                 for _ in range(3):        # several steps: the buffers are reused from step to step
                     st.run()
                 torch.cuda.synchronize()
@@ -58,9 +59,9 @@ def _worker(rank, world, port, q):
                 outs[mode] = st.G.clone()
                 st.close()
         # two ranks: a + b in every implementation
-        same_bits = all(torch.equal(outs["nccl"], outs[x]) for x in ("switch", "rows", "rows_in_parts"))
+        same_bits = all(torch.equal(outs["nccl"], outs[x]) for x in ("switch", "rows", "rows_in_parts", "switch_in_parts"))
         same_across_ranks = True
-        for mode in ("switch", "rows", "rows_in_parts"):
+        for mode in ("switch", "rows", "rows_in_parts", "switch_in_parts"):
             other = outs[mode].clone()
             dist.broadcast(other, src=0)
             same_across_ranks = same_across_ranks and torch.equal(other.view(torch.int32), outs[mode].view(torch.int32))
