@@ -234,8 +234,9 @@ def generate(args, device):
 
 
 def workload_config(problem, args, world, extra=None):
-    cfg = {"workload": "config2+4: LDA-shaped S %dx%d, nnz=%d, k=%d; ops A*S, DDS(A,B,S), B*^S%s"
-                       % (problem.m, problem.n, problem.nnz, problem.k, " + allreduce" if world > 1 else ""),
+    # the same string in both arms and at every N (the line's "allreduce" key names the sum over the ranks)
+    cfg = {"workload": "config2+4: LDA-shaped S %dx%d, nnz=%d, k=%d; ops A*S, DDS(A,B,S), B*^S"
+                       % (problem.m, problem.n, problem.nnz, problem.k),
            "scale": args.scale, "seed": args.seed, "sharding": "columns by equal nnz, A replicated",
            "l2": "inputs larger than L2 (dense operands %.2f GB each)" % (4.0 * problem.k * problem.m / 1e9)}
     if extra:
@@ -538,8 +539,9 @@ def run_b200(args, rank, local_rank, world):
             "dsmult_dds_path": ("one pass over S for A*S and DDS (bidmat_b200_dsmult_dds_async): the gather of A's "
                                 "columns is shared" if fuse else "two calls (dsmult, dds)"),
             "dsmultT_path": ("reference-signature entry point (sorts every call)" if args.no_plan else
-                             "prepared plan: structure sorted once outside the timed region (%.0f ms, %s bytes held), "
-                             "values permuted every call, %s" % (plan_ms, plan_info["bytes"] if plan_info else "?",
+                             "prepared plan: structure sorted once outside the timed region (%.0f ms together with "
+                             "the step's buffers, %s bytes held), values read through the stored positions on "
+                             "every call, %s" % (plan_ms, plan_info["bytes"] if plan_info else "?",
                                                                 "overwrite mode (G not cleared between steps)"
                                                                 if overwrite else "G cleared every step"))}),
         "clocks": clocks, "gpu_launches": int(launches), "roofline": roofline, "e2e": e2e, "verified": verified,
