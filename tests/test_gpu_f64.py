@@ -57,6 +57,29 @@ def test_f64_ops(cuda_device, k, chunk, monkeypatch):
     assert_close_scaled(Pz.cpu().numpy(), want, scale, 1e-13, "f64 DDS0")
 
 
+@pytest.mark.parametrize("k", [64, 256])
+def test_f64_transposed_product_with_column_blocks(cuda_device, k, monkeypatch):
+    """B*^S in fp64 through the reference-signature entry point with the dense operand cut into
+    small column blocks and tiny chunks: the predicate-free kernel on slices of the sorted list."""
+    from bidmat_b200 import _lib
+    L = _lib.lib
+    monkeypatch.setenv("BIDMAT_B200_COLBLOCK_COLS", "32")
+    monkeypatch.setenv("BIDMAT_B200_CHUNK", "32")
+    rng = np.random.default_rng(300 + k)
+    m, n = 70, 150
+    jc, ir, data32 = random_csc(m, n, 0.3, rng, empty_cols=(0, 149))
+    data = data32.astype(np.float64) + rng.uniform(0, 1e-9, len(data32))
+    S = DeviceCSC(m, n, jc, ir, data32, cuda_device)
+    B = rng.standard_normal((n, k))
+    G0 = rng.standard_normal((m, k))
+    G, dB, dd = dev(G0, cuda_device), dev(B, cuda_device), dev(data, cuda_device)
+    assert L.bidmat_b200_dsmultT_f64(k, n, S.nnz, dB.data_ptr(), dd.data_ptr(), S.ir.data_ptr(), S.ic.data_ptr(),
+                                     G.data_ptr()) == 0
+    absS = sp.csc_matrix((np.abs(data), ir, jc), shape=(m, n))
+    assert_close_scaled(G.cpu().numpy(), oracle.dsmultT_d(B, data, ir, jc, m, out=G0.copy()),
+                        absS @ np.abs(B) + np.abs(G0), 1e-12, "f64 B*^S in column blocks")
+
+
 def test_f64_results_are_bit_reproducible_and_noop_on_empty(cuda_device, monkeypatch):
     from bidmat_b200 import _lib
     L = _lib.lib

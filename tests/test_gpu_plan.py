@@ -194,18 +194,19 @@ def test_planned_product_double_precision_at_the_predicate_free_heights(cuda_dev
     absS = np.zeros((m, n))
     np.add.at(absS, (ir, S.ic_h), np.abs(d64))
     scale = absS @ np.abs(B)
-    G = plan.run(dev(B, cuda_device), S, dev(G0, cuda_device), 0, dd).cpu().numpy()
+    dB = dev(B, cuda_device)
+    G = plan.run(dB, S, dev(G0, cuda_device), 0, dd).cpu().numpy()
     want = oracle.dsmultT_d(B, d64, ir, jc, m, out=G0.copy())
     assert_close_scaled(G, want, scale + np.abs(G0), 1e-12, "planned f64 B*^S k=%d" % k)
     # overwrite mode on a dirty buffer: rows the matrix touches equal the product, the others keep their contents
-    Gd = plan.run(dev(B, cuda_device), S, dev(G0, cuda_device), OVERWRITE, dd).cpu().numpy()
+    Gd = plan.run(dB, S, dev(G0, cuda_device), OVERWRITE, dd).cpu().numpy()
     want0 = oracle.dsmultT_d(B, d64, ir, jc, m)
     touched = np.zeros(m, dtype=bool)
     touched[ir] = True
     assert_close_scaled(Gd[touched], want0[touched], scale[touched], 1e-12, "planned f64 overwrite k=%d" % k)
     assert np.array_equal(Gd[~touched], G0[~touched])
     # same bits on a second run
-    G2 = plan.run(dev(B, cuda_device), S, dev(G0, cuda_device), 0, dd).cpu().numpy()
+    G2 = plan.run(dB, S, dev(G0, cuda_device), 0, dd).cpu().numpy()
     assert np.array_equal(G.view(np.int64), G2.view(np.int64))
     plan.close()
 
