@@ -10,8 +10,8 @@ back by BIDMat.
          (HMat.scala:337-365 load, 876-890 save)
 
 Little-endian (HMat.scala:34).  A name ending in .gz is gzip-compressed
-(HMat.scala:86-95).  BIDMat's .lz4 variant uses lz4-java's block stream, for
-which no codec is available here: such files are refused with a clear error.
+(HMat.scala:86-95); a name ending in .lz4 is an lz4-java block stream
+(HMat.scala:90-91, 101-107), read and written by the codec in lz4block.py.
 """
 import gzip
 
@@ -25,8 +25,8 @@ _LE_F32 = np.dtype("<f4")
 
 def _open(fname, mode):
     if fname.endswith(".lz4"):
-        raise RuntimeError("%s: lz4-compressed BIDMat files are not supported (no lz4 block-stream codec); "
-                           "re-save as .smat or .smat.gz" % fname)
+        from .lz4block import LZ4BlockReader, LZ4BlockWriter
+        return LZ4BlockReader(open(fname, "rb")) if "r" in mode else LZ4BlockWriter(open(fname, "wb"))
     return gzip.open(fname, mode) if fname.endswith(".gz") else open(fname, mode)
 
 
