@@ -605,6 +605,24 @@ def run_extras(args, problem, shard, B_local, st, dev, stream):
                                               stream.cuda_stream)
             assert err == 0, _lib.error_string(err)
         out["dsmultT_unprepared_ms"] = time_calls(dropin, stream, 3, 1)
+
+        # (1a) the synchronous native of the reference (no stream, no m, no handle) with plans kept by the
+        # library: fingerprint of the structure on every call, plan built at the second sighting
+        def dropin_kept():
+            G2.zero_()
+            torch.cuda.synchronize(dev)
+            err = L.bidmat_b200_dsmultT(k, shard.n, shard.nnz, B_local.data_ptr(), shard.data.data_ptr(),
+                                        shard.ir.data_ptr(), shard.ic.data_ptr(), G2.data_ptr())
+            assert err == 0, _lib.error_string(err)
+        L.bidmat_b200_set_auto_plan(1)
+        try:
+            out["dsmultT_reference_signature_kept_plan_ms"] = time_calls(dropin_kept, stream, 3, 2)
+            import ctypes
+            info = (ctypes.c_longlong * 6)()
+            L.bidmat_b200_auto_plan_info(info, 6)
+            out["kept_plan_info"] = {"built": int(info[1]), "planned_calls": int(info[2]), "plain_calls": int(info[3])}
+        finally:
+            L.bidmat_b200_set_auto_plan(0)
         del G2
         # (1b) A*S and DDS as two calls (what the one-pass entry point replaces)
         out["dsmult_alone_ms"] = time_calls(st.dsmult, stream, 3, 1)

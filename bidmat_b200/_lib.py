@@ -40,6 +40,8 @@ _SIGNATURES = {
     "bidmat_b200_plan_touched_rows": (_c_int, [_vp, _vp, _vp]),
     "bidmat_b200_plan_destroy": (_c_int, [_vp]),
     "bidmat_b200_set_workspace_limit": (_c_int, [ctypes.c_longlong]),
+    "bidmat_b200_set_auto_plan": (_c_int, [_c_int]),
+    "bidmat_b200_auto_plan_info": (_c_int, [ctypes.POINTER(ctypes.c_longlong), _c_int]),
     "bidmat_b200_dsmult_noalloc": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dds_async": (_c_int, [_c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp]),
     "bidmat_b200_dsmult_dds_async": (_c_int, [_c_int, _c_int, _c_int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

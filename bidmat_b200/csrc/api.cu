@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "../../include/bidmat_b200.h"
+#include "auto_plan.cuh"
 #include "launchers.cuh"
 #include "structure_kernels.cuh"
 #include "edgeops.cuh"
@@ -308,7 +309,11 @@ int bidmat_b200_dsmult(int nrows, int ncols, int nnz, const float *A, const floa
 int bidmat_b200_dsmultT(int nrows, int ncols, int nnz, const float *A, const float *Bdata,
                         const int *Bir, const int *Bic, float *C) {
     if (nrows >= 0 && ncols >= 0 && (nnz == 0 || nrows == 0)) return 0;
-    int e = bidmat_b200_dsmultT_async(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, 0, cudaStreamPerThread);
+    // a structure the library keeps a plan for (bidmat_b200_set_auto_plan) skips the sort
+    int handled = 0, m_seen = 0;
+    int e = auto_plan_dsmultT(4, nrows, ncols, nnz, A, Bdata, Bir, Bic, C, &handled, &m_seen);
+    if (handled || e != 0) return e;
+    e = bidmat_b200_dsmultT_async(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, m_seen, cudaStreamPerThread);
     return finish_sync((cudaError_t)e, cudaStreamPerThread);
 }
 
@@ -359,7 +364,10 @@ int bidmat_b200_dsmult_f64(int nrows, int ncols, int nnz, const double *A, const
 int bidmat_b200_dsmultT_f64(int nrows, int ncols, int nnz, const double *A, const double *Bdata,
                             const int *Bir, const int *Bic, double *C) {
     if (nrows >= 0 && ncols >= 0 && (nnz == 0 || nrows == 0)) return 0;
-    int e = dsmultT_impl<double>(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, 0, cudaStreamPerThread);
+    int handled = 0, m_seen = 0;
+    int e = auto_plan_dsmultT(8, nrows, ncols, nnz, A, Bdata, Bir, Bic, C, &handled, &m_seen);
+    if (handled || e != 0) return e;
+    e = dsmultT_impl<double>(nrows, ncols, nnz, A, Bdata, Bir, Bic, C, m_seen, cudaStreamPerThread);
     return finish_sync((cudaError_t)e, cudaStreamPerThread);
 }
 

@@ -209,6 +209,21 @@ BIDMAT_B200_API int bidmat_b200_plan_clear_untouched(bidmat_b200_plan_t plan, in
                                                      bidmat_stream_t stream);
 BIDMAT_B200_API int bidmat_b200_plan_destroy(bidmat_b200_plan_t plan);
 
+/* Plans kept by the library, for a binding that cannot hold a handle (the natives of CUMAT.java:152
+ * rebound as they are).  With set_auto_plan(1), or BIDMAT_B200_AUTO_PLAN=1 in the environment, the
+ * SYNCHRONOUS entry points bidmat_b200_dsmultT and bidmat_b200_dsmultT_f64 take a 128-bit
+ * fingerprint of (Bir, Bic) on every call (one coalesced pass over the two arrays and a 24-byte
+ * read-back), build a plan for a structure when they see it for the second time, and run every later
+ * call whose nrows, ncols, nnz, element type and fingerprint match through it, accumulating like the
+ * ordinary path (same tolerance; the order of the additions is the plan's).  At most 2 plans are kept
+ * per GPU (least recently used goes first); a structure seen only once costs no plan.  Pointers are
+ * never part of the key.  Off by default: a kept plan holds about 13 bytes per nonzero of device
+ * memory.  set_auto_plan(0) switches it off and frees the kept plans.
+ * auto_plan_info fills out[0..count): enabled, plans built, calls that ran through a plan, calls that
+ * took the ordinary path while it was on, plans kept now, device bytes they hold. */
+BIDMAT_B200_API int bidmat_b200_set_auto_plan(int enable);
+BIDMAT_B200_API int bidmat_b200_auto_plan_info(long long *out, int count);
+
 /* A*S without any allocation.  No counterpart in the reference: BIDMat's
  * launchers never needed scratch memory.  It exists for callers that cannot let a
  * library allocate on the device: host applications that have handed all device

@@ -286,3 +286,91 @@ def test_workspace_limit_refuses_on_the_host_and_leaves_the_library_usable(cuda_
     assert_close_scaled(Gd, oracle.dsmultT(B.cpu().numpy(), data, ir, jc, m), Gabs, RTOL_DSMULTT, "after limit")
     assert L.bidmat_b200_workspace_bytes() > 0
     assert L.bidmat_b200_release_workspace() == 0
+
+
+def _auto_info():
+    out = (ctypes.c_longlong * 6)()
+    assert L.bidmat_b200_auto_plan_info(out, 6) == 0
+    return dict(zip(("enabled", "built", "planned_calls", "plain_calls", "kept", "bytes"), [int(v) for v in out]))
+
+
+def test_plans_kept_by_the_library_behind_the_reference_signature(cuda_device):
+    """bidmat_b200_set_auto_plan: the synchronous natives recognise a structure by its fingerprint,
+    build a plan at the second sighting and use it from then on; other structures, other heights
+    and structures seen once take the ordinary path; results as the ordinary path's."""
+    rng = np.random.default_rng(21)
+    k, m, n = 128, 300, 260
+    jc, ir, data = random_csc(m, n, 0.1, rng, empty_cols=(7,))
+    S = DeviceCSC(m, n, jc, ir, data, cuda_device)
+    B = rng.standard_normal((n, k)).astype(np.float32)
+    G0 = rng.standard_normal((m, k)).astype(np.float32)
+    dB = dev(B, cuda_device)
+    want = oracle.dsmultT(B, data, ir, jc, m, out=G0.copy())
+    _, scale = oracle.dsmultT_f64(B, data, ir, jc, m)
+
+    def call(Sx, values=None, kk=k, dBx=None):
+        G = dev(G0[:, :kk].copy() if kk != k else G0, cuda_device)
+        vals = Sx.data if values is None else values
+        assert L.bidmat_b200_dsmultT(kk, Sx.n, Sx.nnz, (dB if dBx is None else dBx).data_ptr(), vals.data_ptr(),
+                                     Sx.ir.data_ptr(), Sx.ic.data_ptr(), G.data_ptr()) == 0
+        return G.cpu().numpy()
+
+    plain = call(S)                                    # switched off: the ordinary path
+    assert _auto_info()["enabled"] == 0
+    assert L.bidmat_b200_set_auto_plan(1) == 0
+    try:
+        base = _auto_info()
+        outs = [call(S) for _ in range(4)]
+        info = _auto_info()
+        assert info["built"] - base["built"] == 1 and info["kept"] == 1 and info["bytes"] > 0
+        assert info["plain_calls"] - base["plain_calls"] == 1 and info["planned_calls"] - base["planned_calls"] == 3
+        for G in outs:
+            assert_close_scaled(G, want, scale + np.abs(G0), RTOL_DSMULTT, "kept plan")
+        assert np.array_equal(outs[0].view(np.uint32), plain.view(np.uint32))          # first sighting: ordinary path
+        assert np.array_equal(outs[1].view(np.uint32), outs[3].view(np.uint32))          # planned calls repeat bit for bit
+        # other values on the same structure (a DDS result): same plan
+        data2 = rng.standard_normal(S.nnz).astype(np.float32)
+        G2 = call(S, dev(data2, cuda_device))
+        _, scale2 = oracle.dsmultT_f64(B, data2, ir, jc, m)
+        assert_close_scaled(G2, oracle.dsmultT(B, data2, ir, jc, m, out=G0.copy()), scale2 + np.abs(G0), RTOL_DSMULTT,
+                            "kept plan, other values")
+        assert _auto_info()["planned_calls"] - base["planned_calls"] == 4
+        # a different structure of the same sizes: rows of two nonzeros of one column exchanged with unused rows
+        ir3 = ir.copy()
+        c = int(np.argmax(np.diff(jc)))
+        free = np.setdiff1d(np.arange(m), ir[jc[c]:jc[c + 1]])[:2]
+        ir3[jc[c]:jc[c] + 2] = free
+        S3 = DeviceCSC(m, n, jc, ir3, data, cuda_device)
+        before = _auto_info()
+        G3 = call(S3)
+        after = _auto_info()
+        assert after["plain_calls"] - before["plain_calls"] == 1 and after["built"] == before["built"]
+        _, scale3 = oracle.dsmultT_f64(B, data, ir3, jc, m)
+        assert_close_scaled(G3, oracle.dsmultT(B, data, ir3, jc, m, out=G0.copy()), scale3 + np.abs(G0), RTOL_DSMULTT,
+                            "other structure")
+        # structures that come by once never cost a plan and do not push the kept one out
+        for i in range(10):
+            jcx, irx, datax = random_csc(m, n, 0.1, np.random.default_rng(1000 + i))
+            Sx = DeviceCSC(m, n, jcx, irx, datax, cuda_device)
+            Gx = call(Sx)
+            _, sx = oracle.dsmultT_f64(B, datax, irx, jcx, m)
+            assert_close_scaled(Gx, oracle.dsmultT(B, datax, irx, jcx, m, out=G0.copy()), sx + np.abs(G0), RTOL_DSMULTT,
+                                "passing structure %d" % i)
+        assert _auto_info()["built"] == after["built"]
+        before = _auto_info()
+        assert np.array_equal(call(S).view(np.uint32), outs[1].view(np.uint32))
+        assert _auto_info()["planned_calls"] - before["planned_calls"] == 1
+        # the double-precision native keeps plans of its own
+        B64, d64, G064 = B.astype(np.float64), data.astype(np.float64), G0.astype(np.float64)
+        dB64, dd64 = dev(B64, cuda_device), dev(d64, cuda_device)
+        for i in range(3):
+            G = dev(G064, cuda_device)
+            assert L.bidmat_b200_dsmultT_f64(k, n, S.nnz, dB64.data_ptr(), dd64.data_ptr(), S.ir.data_ptr(),
+                                             S.ic.data_ptr(), G.data_ptr()) == 0
+            assert_close_scaled(G.cpu().numpy(), oracle.dsmultT_d(B64, d64, ir, jc, m, out=G064.copy()),
+                                scale + np.abs(G064), 1e-12, "kept plan, fp64, call %d" % i)
+        assert _auto_info()["kept"] == 2
+    finally:
+        assert L.bidmat_b200_set_auto_plan(0) == 0
+    info = _auto_info()
+    assert info["enabled"] == 0 and info["kept"] == 0 and info["bytes"] == 0
