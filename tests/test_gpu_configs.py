@@ -8,10 +8,21 @@ import torch
 
 import oracle
 from bidmat_b200 import gen
-from util import RTOL_DDS, RTOL_DSMULT, RTOL_DSMULTT, assert_close_scaled
+from util import RTOL_DDS, RTOL_DSMULT, RTOL_DSMULTT, assert_close_scaled, error_summary
 from gpu_util import DeviceCSC, abi_dds, abi_dsmult, abi_dsmultT
 
 pytestmark = pytest.mark.gpu
+
+
+def _report(name, op, rtol, got, want32, want64, scale):
+    """Acceptance (rtol * sum|terms| against the fp32 CPU loops), the same bound against the fp64
+    oracle, and the figures to report beside them (printed: run pytest with -s to see them)."""
+    assert_close_scaled(got, want32, scale, rtol, name + " " + op)
+    assert_close_scaled(got, want64, scale, rtol, name + " " + op + " against fp64")
+    e = error_summary(got, want32, want64, scale)
+    print("PARITY %s | %s | gpu-cpu32 %.2e | gpu-fp64 %.2e | cpu32-fp64 %.2e | max rel (significant, %.0f%%) %.2e"
+          % (name, op, e["gpu_vs_cpu32_over_sumabs"], e["gpu_vs_fp64_over_sumabs"], e["cpu32_vs_fp64_over_sumabs"],
+             100 * e["significant_fraction"], e["max_rel_err_significant"]))
 
 
 def run_problem(p, device, check_T=True):
@@ -21,15 +32,15 @@ def run_problem(p, device, check_T=True):
     A, B = p.A.to(device), p.B.to(device)
     Ah, Bh = p.A.cpu().numpy(), p.B.cpu().numpy()
     C = abi_dsmult(A, S, torch.zeros((p.n, p.k), device=device)).cpu().numpy()
-    _, Cabs = oracle.dsmult_f64(Ah, data, ir, jc)
-    assert_close_scaled(C, oracle.dsmult(Ah, data, ir, jc), Cabs, RTOL_DSMULT, p.name + " A*S")
+    C64, Cabs = oracle.dsmult_f64(Ah, data, ir, jc)
+    _report(p.name, "A*S", RTOL_DSMULT, C, oracle.dsmult(Ah, data, ir, jc), C64, Cabs)
     P = abi_dds(A, B, S, torch.zeros(S.nnz, device=device)).cpu().numpy()
-    _, Pabs = oracle.dds_f64(Ah, Bh, ir, jc)
-    assert_close_scaled(P, oracle.dds(Ah, Bh, ir, jc), Pabs, RTOL_DDS, p.name + " DDS")
+    P64, Pabs = oracle.dds_f64(Ah, Bh, ir, jc)
+    _report(p.name, "DDS", RTOL_DDS, P, oracle.dds(Ah, Bh, ir, jc), P64, Pabs)
     if check_T:
         G = abi_dsmultT(B, S, torch.zeros((p.m, p.k), device=device)).cpu().numpy()
-        _, Gabs = oracle.dsmultT_f64(Bh, data, ir, jc, p.m)
-        assert_close_scaled(G, oracle.dsmultT(Bh, data, ir, jc, p.m), Gabs, RTOL_DSMULTT, p.name + " B*^S")
+        G64, Gabs = oracle.dsmultT_f64(Bh, data, ir, jc, p.m)
+        _report(p.name, "B*^S", RTOL_DSMULTT, G, oracle.dsmultT(Bh, data, ir, jc, p.m), G64, Gabs)
 
 
 def test_config1_full_size(cuda_device):

@@ -40,3 +40,22 @@ def assert_close_scaled(got, want, scale, rtol, what=""):
                              "(got %r want %r scale %r)" % (what, int(bad.sum()), bad.size, rtol,
                                                             float((err / bound).flat[i]), got.flat[i],
                                                             want.flat[i], np.asarray(scale).flat[i]))
+
+
+def error_summary(got, want32, want64, scale):
+    """The figures reported beside the acceptance rule: the worst error of the result against
+    the fp32 CPU loops and against the fp64 oracle, both in units of sum|terms|, the same for the
+    CPU loops against fp64, and the largest relative error over the elements that are not
+    cancellation leftovers (|cpu| > 1e-3 * sum|terms|)."""
+    got = np.asarray(got, dtype=np.float64).ravel()
+    want32 = np.asarray(want32, dtype=np.float64).ravel()
+    want64 = np.asarray(want64, dtype=np.float64).ravel()
+    scale = np.asarray(scale, dtype=np.float64).ravel() + 1e-300
+    big = np.abs(want32) > 1e-3 * scale
+    return {
+        "gpu_vs_cpu32_over_sumabs": float(np.max(np.abs(got - want32) / scale)),
+        "gpu_vs_fp64_over_sumabs": float(np.max(np.abs(got - want64) / scale)),
+        "cpu32_vs_fp64_over_sumabs": float(np.max(np.abs(want32 - want64) / scale)),
+        "max_rel_err_significant": float(np.max(np.abs(got - want32)[big] / np.abs(want32)[big])) if big.any() else 0.0,
+        "significant_fraction": float(big.mean()),
+    }
