@@ -201,16 +201,16 @@ int spsum_impl(int nrows, int ncols, int nnz, const int *Air, const int *Aic, co
     int rowbits = ceil_log2((unsigned long long)(nrows > 0 ? nrows : 1));
     if (rowbits < 1) rowbits = 1;
     if (rowbits > 31) return (int)cudaErrorInvalidValue;
-    WorkspaceLease ws(4 * pad256(n_ * 4) + 2 * pad256(n_ * sizeof(S)) + pad256((size_t)256 * ntiles * 4) +
+    WorkspaceLease ws(2 * pad256(n_ * 4) + 2 * pad256(n_ * sizeof(S)) + pad256((size_t)256 * ntiles * 4) +
                           pad256(256 * kSortScanSegs * 4) + pad256(part_elems * sizeof(S)) + 4096, st);
     if (ws.err != cudaSuccess) return (int)ws.err;
     unsigned *keys[2] = {ws.take<unsigned>(n_), ws.take<unsigned>(n_)};
-    int *cols[2] = {ws.take<int>(n_), ws.take<int>(n_)};
+    int *cols[2] = {nullptr, nullptr};          // the sums need no columns: (row, value) pairs are sorted
     S *vals[2] = {ws.take<S>(n_), ws.take<S>(n_)};
     int *counts = ws.take<int>((size_t)256 * ntiles);
     int *totals = ws.take<int>(256 * kSortScanSegs);
     S *part = ws.take<S>(part_elems);
-    const int cur = run_rowsort<S>(nnz, (rowbits + 7) / 8, SortKeySpec{31, rowbits}, Air, Aic, P, keys, cols, vals,
+    const int cur = run_rowsort<S>(nnz, (rowbits + 7) / 8, SortKeySpec{31, rowbits}, Air, nullptr, P, keys, cols, vals,
                                    nullptr, nullptr, nullptr, counts, totals, st);
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return (int)err;

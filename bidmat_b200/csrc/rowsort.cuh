@@ -37,7 +37,8 @@ __device__ __forceinline__ unsigned make_sort_key(int row, int col, SortKeySpec 
 
 // FIRST: keys are computed from (ir, ic); otherwise read from keys_in.  In the first
 // scatter pass a null value array makes the position of each nonzero its payload,
-// which gives the permutation the sort applies.
+// which gives the permutation the sort applies.  A null column array (in and out)
+// sorts (row, value) pairs only: 16 instead of 24 bytes per key and pass.
 template <bool FIRST>
 __global__ void __launch_bounds__(kSortThreads)
 sort_hist_kernel(long long n, int ntiles, int shift, SortKeySpec ks, const unsigned *__restrict__ keys_in,
@@ -55,7 +56,7 @@ sort_hist_kernel(long long n, int ntiles, int shift, SortKeySpec ks, const unsig
     for (int i = 0; i < kSortKeysPerThread; i++) {
         const long long j = base + i * kSortThreads + threadIdx.x;
         if (j < n) {
-            const unsigned key = FIRST ? make_sort_key(__ldg(ir + j), __ldg(ic + j), ks) : __ldg(keys_in + j);
+            const unsigned key = FIRST ? make_sort_key(__ldg(ir + j), ic ? __ldg(ic + j) : 0, ks) : __ldg(keys_in + j);
             const unsigned d = (key >> shift) & 255u;
             if (d == prev) {
                 run++;
@@ -170,7 +171,7 @@ sort_scatter_kernel(long long n, int ntiles, int shift, SortKeySpec ks, const un
         pb[r] = 0;
         if (ok) {
             const long long j = tile_base + pos;
-            pa[r] = __ldg(a_in + j);
+            pa[r] = a_in ? __ldg(a_in + j) : 0;          // no column payload: rows and values only
             pb[r] = b_in ? __ldg(b_in + j) : (PV)j;      // no payload given: the position itself
             key[r] = FIRST ? make_sort_key(__ldg(ir + j), pa[r], ks) : __ldg(keys_in + j);
         }
@@ -240,7 +241,7 @@ sort_scatter_kernel(long long n, int ntiles, int shift, SortKeySpec ks, const un
         const unsigned d = (kk >> shift) & 255u;
         const long long out = (long long)sm.global_base[d] + (i - sm.digit_start[d]);
         keys_out[out] = kk;
-        a_out[out] = sm.a[i];
+        if (a_out) a_out[out] = sm.a[i];
         b_out[out] = sm.b[i];
     }
 }
